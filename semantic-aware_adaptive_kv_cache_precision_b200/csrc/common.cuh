@@ -1,0 +1,68 @@
+// Shared by every kernel file: element types, widening and narrowing, warp and
+// block reductions, and the launch-error convention of the exported functions.
+//
+// Every exported function is `extern "C"`, takes raw device pointers, sizes and
+// a stream, launches without synchronising, and returns a cudaError_t as int
+// (0 = launched). Sizes a kernel cannot take are refused with
+// cudaErrorInvalidValue before anything is launched; the Python side turns a
+// non-zero code into an exception that names the function.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define SAKV_EXPORT extern "C" __attribute__((visibility("default")))
+
+// dtype codes shared with the Python side (ops/_lib.py)
+enum : int { SAKV_F32 = 0, SAKV_BF16 = 1 };
+
+constexpr int kCacheBlock = 64;  // tokens per cache block; the Python side asserts the same
+
+__device__ __forceinline__ float widen(float v) { return v; }
+__device__ __forceinline__ float widen(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T narrow(float v);
+template <> __device__ __forceinline__ float narrow<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 narrow<__nv_bfloat16>(float v) {
+  return __float2bfloat16_rn(v);
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Sum over a block of up to 1024 threads; every thread gets the result. The
+// order of the additions depends on the block size only.
+__device__ __forceinline__ float block_sum(float v, float* scratch /* >= 33 floats */) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int warps = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float total = 0.f;
+    for (int w = 0; w < warps; ++w) total += scratch[w];
+    scratch[32] = total;
+  }
+  __syncthreads();
+  return scratch[32];
+}
+
+static inline int launch_status() { return static_cast<int>(cudaGetLastError()); }
+
+static inline int grid_for(long long work, int threads, int cap = 148 * 16) {
+  long long blocks = (work + threads - 1) / threads;
+  if (blocks < 1) blocks = 1;
+  if (blocks > cap) blocks = cap;
+  return static_cast<int>(blocks);
+}

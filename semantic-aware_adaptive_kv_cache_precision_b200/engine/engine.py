@@ -1,0 +1,302 @@
+"""The engine: a model, its cache, the step function and the generation loop.
+
+The Python entry point follows the reference's `Engine`
+(`src/microinfer/engine.py:822-833, 927-974, 1157-1206`): `Engine(model_dir)`,
+`load_weights()`, `generate(prompt, max_new_tokens=64, *, stop_at_eos=True,
+report=None)`, `forward(token_ids)`, `eos_token_ids`, `ending`. Where the
+reference runs one sequence, this engine runs batches: `generate` also takes a
+list of prompts, and `step` feeds any batch of sequences that start together.
+"""
+
+from __future__ import annotations
+
+import json
+from pathlib import Path
+
+import numpy as np
+import torch
+
+from .. import sampling
+from ..cache import BLOCK, CacheFull, SequenceCache
+from ..config import config_from_dict, config_from_folder
+from .generate import (COMPLETE, DECODING, EXHAUSTED, PREFILLING, Ending, RequestState,
+                       check_prompt, check_window, plan_batches, plan_prefill, positions_needed)
+from .model import DecoderModel
+from .step import StepStager
+
+DEFAULT_MAX_TOKENS = 16384
+DEFAULT_MAX_BATCH = 64
+DEFAULT_MAX_STEP_TOKENS = 16384
+
+
+class Engine:
+    """`model_dir`: a folder with config.json and model.safetensors. Instead of a
+    folder, `config=` (a config.json dict or a configuration object) with
+    `random_seed=` builds the model with random weights on the device.
+
+    `dtype`: 'bfloat16' (the serving kernels) or 'float32' (everything in true
+    32-bit). `max_tokens`: cache positions over all live sequences, each
+    sequence counted in blocks of 64. `max_batch`: most sequences in one batch.
+    """
+
+    def __init__(self, model_dir=None, *, config=None, dtype: str = "bfloat16",
+                 max_tokens: int = DEFAULT_MAX_TOKENS, max_batch: int = DEFAULT_MAX_BATCH,
+                 max_step_tokens: int = DEFAULT_MAX_STEP_TOKENS, random_seed: int | None = None,
+                 device="cuda", poison_freed: bool = False):
+        if not torch.cuda.is_available():
+            raise RuntimeError("no CUDA device: this library runs its own sm_100a kernels "
+                               "and has no CPU implementation")
+        if (model_dir is None) == (config is None):
+            raise ValueError("give either a model folder or config=")
+        self.model_dir = None if model_dir is None else Path(model_dir)
+        if config is None:
+            self.config = config_from_folder(self.model_dir)
+        else:
+            self.config = config_from_dict(config) if isinstance(config, dict) else config
+        self.dtype = {"bf16": "bfloat16", "fp32": "float32"}.get(dtype, dtype)
+        self.device = torch.device(device)
+        self.random_seed = random_seed
+        self.max_tokens, self.max_batch = int(max_tokens), int(max_batch)
+        self.max_step_tokens = int(max_step_tokens)
+        self.poison_freed = poison_freed
+        self.spec = self.config.model_spec()
+        self.model = DecoderModel(self.spec, self.dtype, self.device)
+        self.cache: SequenceCache | None = None
+        self._stager = StepStager(self.device)
+        self.ending = None
+        self.endings: list = []
+        self._loaded = False
+
+    # -- loading ----------------------------------------------------------------
+
+    def load_weights(self) -> "Engine":
+        """Check the checkpoint against the configuration, then put every tensor on
+        the device; a model is never half loaded."""
+        with torch.cuda.device(self.device):
+            if self.model_dir is not None:
+                self.model.load(self.model_dir)
+            else:
+                self.model.load_random(0 if self.random_seed is None else self.random_seed)
+        self._loaded = True
+        return self
+
+    def _need_loaded(self) -> None:
+        if not self._loaded:
+            raise RuntimeError("no weights on the device; call load_weights() first")
+
+    def _need_cache(self) -> SequenceCache:
+        if self.cache is None:
+            self._need_loaded()
+            act = torch.float32 if self.dtype == "float32" else torch.bfloat16
+            self.cache = SequenceCache(self.model.cache_needs(), self.max_tokens,
+                                       self.spec.max_positions, act, self.device,
+                                       max_slots=min(-(-self.max_tokens // BLOCK), 4096),
+                                       poison_freed=self.poison_freed)
+            self.model.prepare(self.cache.max_seq_len)
+        return self.cache
+
+    @property
+    def vocab_size(self) -> int:
+        return self.spec.vocab_size
+
+    @property
+    def eos_token_ids(self) -> frozenset:
+        """generation_config.json's eos_token_id if the folder has one
+        (`src/microinfer/engine.py:1148-1153`), else config.json's."""
+        if self.model_dir is not None:
+            path = self.model_dir / "generation_config.json"
+            if path.is_file():
+                eos = json.loads(path.read_text()).get("eos_token_id")
+                if eos is not None:
+                    return frozenset(eos if isinstance(eos, list) else [eos])
+        return frozenset(self.spec.stop_token_ids)
+
+    def footprint(self) -> dict:
+        """Bytes on the device: weights, cache, and what the device reports."""
+        free, total = torch.cuda.mem_get_info(self.device)
+        return {"weights": self.model.weight_bytes,
+                "kv_cache": 0 if self.cache is None else self.cache.nbytes,
+                "device_free": free, "device_total": total}
+
+    # -- the step function ----------------------------------------------------------
+
+    def open(self, count: int = 1) -> list[int]:
+        """Take cache slots for `count` new sequences."""
+        return self._need_cache().open(count)
+
+    def close(self, slots) -> None:
+        """End sequences; what they hold goes back to the cache."""
+        self._need_cache().close(slots)
+
+    def step(self, slots: list, new_tokens: list, want: list | None = None) -> torch.Tensor:
+        """Feed `new_tokens[i]` to the sequence in `slots[i]`, after what its cache
+        already holds, all sequences as one batch. Returns fp32 logits
+        [wanted, vocab] on the device for `want[i]`, the places among
+        `new_tokens[i]` whose logits are asked for, in the order of the sequences
+        (default: each sequence's last token)."""
+        cache = self._need_cache()
+        if len(slots) != len(new_tokens) or not slots:
+            raise ValueError("step needs as many token lists as slots, and at least one")
+        if len(set(slots)) != len(slots):
+            raise ValueError("a sequence appears twice in one step")
+        counts = [len(t) for t in new_tokens]
+        if min(counts) <= 0:
+            raise ValueError("every sequence of a step must bring at least one token")
+        starts = [int(cache.lengths[s]) for s in slots]
+        ends = [s + c for s, c in zip(starts, counts)]
+        if want is None:
+            want = [[c - 1] for c in counts]
+        rows, base = [], 0
+        for w, c in zip(want, counts):
+            for p in w:
+                if not 0 <= p < c:
+                    raise ValueError(f"wanted place {p} is outside the {c} tokens brought")
+                rows.append(base + p)
+            base += c
+        with torch.cuda.device(self.device):
+            cache.reserve(slots, ends)
+            ctx = self._stager.build(slots, new_tokens, starts, rows, cache.tables_for(slots))
+            x = self.model.hidden(ctx, cache)
+            cache.advance(slots, ends)
+            if not rows:
+                return torch.empty((0, self.spec.vocab_size), dtype=torch.float32,
+                                   device=self.device)
+            return self.model.logits(x, ctx.want)
+
+    # -- whole sequences ---------------------------------------------------------------
+
+    def forward(self, token_ids) -> np.ndarray:
+        """fp32 logits (seq, vocab) for every position of one sequence
+        (`src/microinfer/engine.py:1157-1178`)."""
+        self._need_loaded()
+        ids = check_prompt(token_ids, self.spec.vocab_size)
+        check_window(len(ids), self.spec.max_positions)
+        (slot,) = self.open(1)
+        try:
+            out = []
+            for begin in range(0, len(ids), self.max_step_tokens):
+                chunk = ids[begin:begin + self.max_step_tokens]
+                out.append(self.step([slot], [chunk], [list(range(len(chunk)))]).cpu().numpy())
+            return np.concatenate(out)
+        finally:
+            self.close([slot])
+
+    # -- generation -------------------------------------------------------------------------
+
+    def generate(self, prompt, max_new_tokens: int = 64, *, stop_at_eos: bool = True,
+                 report=None, temperature: float = 0.0, seed: int = 0, stop_token_ids=None):
+        """New token ids for one prompt (a 1-D sequence of ids: returns one int32
+        array) or for a list of prompts (returns a list of int32 arrays).
+
+        Prompts are taken in batches that start together; each batch prefills all
+        its prompts in one step and then decodes one token per live request a
+        step. A request ends after `max_new_tokens` or at a stop token, which is
+        kept (`stop_at_eos`: the model's end-of-sequence ids; `stop_token_ids`
+        replaces them), and leaves its batch at once. `temperature` 0 is greedy.
+        `report(phase, positions, token)` is called after each prefill with token
+        None and after each decoded token; for a list of prompts it gets the
+        request's number as a fourth argument. `self.ending` (one prompt) or
+        `self.endings` say how each request ended.
+        """
+        self._need_loaded()
+        single = not _is_list_of_sequences(prompt)
+        prompts = [prompt] if single else list(prompt)
+        if max_new_tokens < 0:
+            raise ValueError(f"max_new_tokens must not be negative, got {max_new_tokens}")
+        ids = [check_prompt(p, self.spec.vocab_size, f"prompt {i}" if not single else "token_ids")
+               for i, p in enumerate(prompts)]
+        params = sampling.SamplingParams(float(temperature), int(seed))
+        if max_new_tokens == 0:
+            self.endings = [Ending(COMPLETE, 0, np.empty(0, np.int32), "length") for _ in ids]
+            self.ending = self.endings[0] if single else None
+            return self.endings[0].tokens if single else [e.tokens for e in self.endings]
+        for p in ids:
+            check_window(positions_needed(len(p), max_new_tokens), self.spec.max_positions)
+        if stop_token_ids is not None:
+            stops = frozenset(int(t) for t in stop_token_ids)
+        else:
+            stops = self.eos_token_ids if stop_at_eos else frozenset()
+        if report is None:
+            tell = lambda *a: None
+        elif single:
+            tell = lambda phase, positions, token, request: report(phase, positions, token)
+        else:
+            tell = report
+
+        cache = self._need_cache()
+        batches = plan_batches([len(p) for p in ids], max_new_tokens, self.max_batch,
+                               cache.max_tokens)
+        endings: dict[int, Ending] = {}
+        for batch in batches:
+            self._run_batch([RequestState(i, ids[i]) for i in batch], max_new_tokens, stops,
+                            params, tell, endings)
+        self.endings = [endings[i] for i in range(len(ids))]
+        self.ending = self.endings[0] if single else None
+        return self.endings[0].tokens if single else [e.tokens for e in self.endings]
+
+    def _run_batch(self, requests, max_new_tokens, stops, params, tell, endings) -> None:
+        cache = self._need_cache()
+        slots = cache.open(len(requests))
+        slot_of = {r.index: s for r, s in zip(requests, slots)}
+        live = list(requests)
+
+        def finish(r, state=COMPLETE, reason=None):
+            endings[r.index] = Ending(state, int(cache.lengths[slot_of[r.index]]),
+                                      np.asarray(r.out, np.int32), reason or r.reason)
+            cache.close([slot_of[r.index]])
+
+        try:
+            # prefill: every prompt whole, in one step unless the batch is too large
+            plans = plan_prefill([len(r.prompt) for r in requests], self.max_step_tokens)
+            logits = {}
+            for plan in plans:
+                step_slots = [slots[i] for i, _, _ in plan]
+                tokens = [requests[i].prompt[a:a + n] for i, a, n in plan]
+                ends = [a + n == len(requests[i].prompt) for i, a, n in plan]
+                want = [[n - 1] if last else [] for (_, _, n), last in zip(plan, ends)]
+                out = self.step(step_slots, tokens, want)
+                row = 0
+                for (i, _, _), last in zip(plan, ends):
+                    if last:
+                        logits[i] = out[row]
+                        row += 1
+            first = torch.stack([logits[i] for i in range(len(requests))])
+            chosen = self._choose(first, params, live)
+            for r, token in zip(live, chosen):
+                tell(PREFILLING, len(r.prompt), None, r.index)
+                r.accept(token, stops, max_new_tokens)
+            for r in [r for r in live if r.finished]:
+                finish(r)
+            live = [r for r in live if not r.finished]
+            # decode: one token for each live request a step
+            while live:
+                out = self.step([slot_of[r.index] for r in live],
+                                [np.asarray(r.out[-1:], np.int32) for r in live])
+                chosen = self._choose(out, params, live)
+                for r, token in zip(live, chosen):
+                    r.accept(token, stops, max_new_tokens)
+                    tell(DECODING, int(cache.lengths[slot_of[r.index]]), int(token), r.index)
+                for r in [r for r in live if r.finished]:
+                    finish(r)
+                live = [r for r in live if not r.finished]
+        except CacheFull as exc:
+            for r in live:
+                finish(r, EXHAUSTED, str(exc))
+        except BaseException:
+            held = [slot_of[r.index] for r in requests if r.index not in endings]
+            cache.close(held)
+            raise
+
+    def _choose(self, logits, params, live) -> list[int]:
+        tokens = sampling.choose(logits, params, [r.index for r in live],
+                                 [len(r.out) for r in live]).cpu().tolist()
+        sampling.check_chosen(tokens, self.spec.vocab_size)
+        return tokens
+
+
+def _is_list_of_sequences(prompt) -> bool:
+    if isinstance(prompt, np.ndarray):
+        return False              # an array is one prompt; a 2-D one is refused as such
+    if isinstance(prompt, (list, tuple)) and prompt:
+        return isinstance(prompt[0], (list, tuple, np.ndarray))
+    return False

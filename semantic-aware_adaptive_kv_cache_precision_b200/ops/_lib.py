@@ -1,0 +1,76 @@
+"""ctypes access to the compiled kernels: signatures, stream and error handling."""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_ulonglong, c_void_p
+
+import torch
+
+from ..csrc import build as _build
+
+F32, BF16 = 0, 1
+CACHE_BLOCK = 64          # tokens per cache block; csrc/common.cuh has the same constant
+
+
+class KernelError(RuntimeError):
+    """A kernel refused its arguments or failed to launch."""
+
+
+P, I, L, F, U = c_void_p, c_int, c_longlong, c_float, c_ulonglong
+
+#: exported function -> (library, argument types); the stream is always last
+SIGNATURES = {
+    "sakv_embed": ("elementwise", [P, P, I, P, I, I, I, P]),
+    "sakv_gated_silu": ("elementwise", [P, P, I, I, I, P]),
+    "sakv_add_into": ("elementwise", [P, P, I, L, P]),
+    "sakv_rmsnorm": ("norm", [P, P, P, I, P, I, I, I, F, P]),
+    "sakv_rope_store": ("rope", [P, I, L, P, P, P, I, P, P, I, P, P, I, I, I, I, I, P]),
+    "sakv_attention_plain": ("attention_plain",
+                             [P, I, L, P, P, P, P, P, P, I, I, I, I, I, F, I, P]),
+    "sakv_gemm_f32": ("gemm_f32", [P, L, P, P, P, L, I, I, I, I, P]),
+    "sakv_choose": ("sampling", [P, L, I, I, F, U, P, P, P, P]),
+}
+
+_functions: dict[str, object] = {}
+
+
+def function(name: str):
+    fn = _functions.get(name)
+    if fn is None:
+        library, argtypes = SIGNATURES[name]
+        fn = getattr(_build.load(library), name)
+        fn.argtypes = argtypes
+        fn.restype = c_int
+        _functions[name] = fn
+    return fn
+
+
+def dtype_code(dtype: torch.dtype) -> int:
+    if dtype == torch.float32:
+        return F32
+    if dtype == torch.bfloat16:
+        return BF16
+    raise KernelError(f"kernels take float32 or bfloat16, got {dtype}")
+
+
+def ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+def stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def require_cuda(*tensors) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise KernelError("this library runs on a CUDA device only: got a tensor on "
+                              f"{t.device}; there is no CPU implementation")
+
+
+def call(name: str, *args) -> None:
+    code = function(name)(*args, stream())
+    if code != 0:
+        raise KernelError(f"{name} failed with CUDA error {code}"
+                          + (" (invalid value: a size this kernel does not take)" if code == 1 else ""))

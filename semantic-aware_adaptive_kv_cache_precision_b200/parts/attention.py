@@ -1,0 +1,98 @@
+"""Grouped-query causal self-attention over the cache.
+
+    q, k, v = split(h Wqkv^T + bqkv);  q, k = position(q, k);  cache <- k, v
+    out = softmax(q k^T * scale + mask) v;  residual += out Wo^T (+ bo)
+
+as the reference runs it (`src/microinfer/model.py:375-387`), except that the
+three projections are one product over the rows [Wq; Wk; Wv] laid back to back
+in device memory, and that the key's bias goes through the projection and the
+rotation with the key (the reference adds it, rotated, inside attention, which
+is the same sum; `src/core_kernels/attention.cu:104-116`). The mask lets a
+query at position p see keys j <= p, and only those with p - j < window where
+the spec has a window. Sizes, scale, window and whether there are biases come
+from the spec.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from ..cache.needs import KVNeed
+from ..weights.decl import TensorDecl
+from .base import Part, build_part, register_part
+
+
+class GQAAttention(Part):
+    def __init__(self, spec, prefix, mode):
+        super().__init__(spec, prefix, mode)
+        s = spec
+        if s.heads % s.kv_heads:
+            raise ValueError(f"{s.heads} heads are not a multiple of {s.kv_heads} kv heads")
+        if s.head_dim % 16 or s.head_dim > 256:
+            raise ValueError(f"head_dim {s.head_dim}: the attention kernels take multiples "
+                             "of 16 up to 256")
+        self.position = build_part(s.position, prefix, mode) if s.position is not None \
+            else build_part(_NO_POSITION, prefix, mode)
+
+    # -- tensors --------------------------------------------------------------
+
+    def tensor_decls(self):
+        s, p = self.spec, self.prefix
+        q, kv = s.heads * s.head_dim, s.kv_heads * s.head_dim
+        decls = []
+        for name, rows in (("q_proj", q), ("k_proj", kv), ("v_proj", kv)):
+            decls.append(TensorDecl(f"{p}{name}.weight", (rows, s.hidden), group=p + "qkv.weight"))
+        if s.qkv_bias:
+            for name, rows in (("q_proj", q), ("k_proj", kv), ("v_proj", kv)):
+                decls.append(TensorDecl(f"{p}{name}.bias", (rows,), group=p + "qkv.bias"))
+        decls.append(TensorDecl(f"{p}o_proj.weight", (s.hidden, q)))
+        if s.out_bias:
+            decls.append(TensorDecl(f"{p}o_proj.bias", (s.hidden,)))
+        return decls
+
+    def bind(self, arena):
+        p = self.prefix
+        names = ("q_proj", "k_proj", "v_proj")
+        self.w_qkv = arena.group_view(p + "qkv.weight")
+        if self.w_qkv is None:
+            self.w_qkv = torch.cat([arena.view(f"{p}{n}.weight") for n in names])
+        self.b_qkv = None
+        if self.spec.qkv_bias:
+            self.b_qkv = arena.group_view(p + "qkv.bias")
+            if self.b_qkv is None:
+                self.b_qkv = torch.cat([arena.view(f"{p}{n}.bias") for n in names])
+        self.w_o = arena.view(p + "o_proj.weight")
+        self.b_o = arena.view(p + "o_proj.bias") if self.spec.out_bias else None
+
+    def prepare(self, device, max_positions):
+        self.position.prepare(device, max_positions)
+
+    # -- cache ----------------------------------------------------------------
+
+    def cache_need(self):
+        return KVNeed(self.spec.kv_heads, self.spec.head_dim, self.spec.window)
+
+    # -- the step ---------------------------------------------------------------
+
+    def forward(self, h, step, view, residual, write_cache=True):
+        s = self.spec
+        qkv = ops.linear(h, self.w_qkv, self.b_qkv, out_dtype=self.act_dtype)
+        self.position.rotate_store(qkv, step, view, s.heads, s.kv_heads, s.head_dim, write_cache)
+        attended = self.attend(qkv, step, view)
+        ops.linear(attended, self.w_o, self.b_o, accumulate_into=residual)
+
+    def attend(self, qkv, step, view):
+        s = self.spec
+        return ops.attention_plain(qkv, view.keys, view.values, step.positions, step.token_seq,
+                                   view.block_table, s.heads, s.kv_heads, s.head_dim, s.scale,
+                                   s.window)
+
+
+class _NoPositionSpec:
+    kind = "no_position"
+
+
+_NO_POSITION = _NoPositionSpec()
+
+register_part("gqa_attention", GQAAttention)

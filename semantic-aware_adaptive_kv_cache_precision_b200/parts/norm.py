@@ -1,0 +1,24 @@
+"""RMSNorm: `x * rsqrt(mean(x^2) + eps) * w` over rows of the fp32 residual
+stream (`src/core_kernels/rmsnorm.cu:33-84`; the weight multiplies directly)."""
+
+from __future__ import annotations
+
+from .. import ops
+from ..weights.decl import TensorDecl
+from .base import Part, register_part
+
+
+class RMSNorm(Part):
+    """`prefix` is the tensor's name without '.weight'."""
+
+    def tensor_decls(self):
+        return [TensorDecl(self.prefix + ".weight", (self.spec.size,), init="ones_normal")]
+
+    def bind(self, arena):
+        self.weight = arena.view(self.prefix + ".weight")
+
+    def forward(self, x, out_dtype=None, rows=None):
+        return ops.rms_norm(x, self.weight, self.spec.eps, out_dtype or self.act_dtype, rows)
+
+
+register_part("rms_norm", RMSNorm)
