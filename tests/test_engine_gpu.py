@@ -1,0 +1,240 @@
+"""The engine against the plain implementation, in 32-bit and in bfloat16: whole
+prompts, the last 32 tokens one by one, batches of unequal lengths with slots
+used again, long decoding, the first tokens of a sequence, and generation."""
+
+import numpy as np
+import pytest
+import torch
+
+import plain_model as plain
+from conftest import TINY, prompts_for
+from helpers import assert_close_to_plain, assert_same_logits, plain_logits
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = ["float32", "bfloat16"]
+NAMES = ["A", "B", "W"]
+
+
+def engine_for(folder, dtype, **kw):
+    from semantic_aware_adaptive_kv_cache_precision_b200 import Engine
+    kw.setdefault("max_tokens", 2048)
+    return Engine(folder, dtype=dtype, poison_freed=True, **kw).load_weights()
+
+
+def stored(dtype):
+    return "float32" if dtype == "float32" else "bfloat16"
+
+
+@pytest.fixture(scope="module")
+def engines(model_folders):
+    made = {}
+
+    def get(name, dtype):
+        if (name, dtype) not in made:
+            made[name, dtype] = engine_for(model_folders(name, stored(dtype)), dtype)
+        return made[name, dtype]
+
+    return get
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", NAMES)
+def test_each_request_alone_and_whole(name, dtype, engines, model_folders):
+    engine = engines(name, dtype)
+    folder = model_folders(name, stored(dtype))
+    lengths = {"A": [5, 11, 17, 100], "B": [1, 7, 30, 64, 200], "W": [3, 69, 70, 71, 150, 300]}[name]
+    for ids in prompts_for(name, lengths):
+        got = engine.forward(ids)
+        assert_close_to_plain(got, plain_logits(folder, ids), dtype, f"{name} len {len(ids)}")
+    engine.cache.check()
+    assert engine.cache.slots.held == 0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", NAMES)
+def test_last_32_tokens_one_by_one(name, dtype, engines, model_folders):
+    engine = engines(name, dtype)
+    folder = model_folders(name, stored(dtype))
+    for ids in prompts_for(name, {"A": [40, 120], "B": [33, 130], "W": [100, 260]}[name], seed=1):
+        whole = engine.forward(ids)
+        (slot,) = engine.open(1)
+        head = len(ids) - 32
+        rows = [engine.step([slot], [ids[:head]], [list(range(head))]).cpu().numpy()]
+        for t in range(head, len(ids)):
+            rows.append(engine.step([slot], [ids[t:t + 1]]).cpu().numpy())
+        engine.close([slot])
+        stepped = np.concatenate(rows)
+        assert_same_logits(stepped, whole, dtype, f"{name} len {len(ids)} stepped vs whole")
+        assert_close_to_plain(stepped, plain_logits(folder, ids), dtype, f"{name} stepped")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", NAMES)
+def test_unequal_batches_one_after_another(name, dtype, model_folders):
+    """Three batches in a cache that holds barely one of them: every slot and block
+    is used again, freed blocks are filled with NaN, and the shorter requests of
+    a batch end while the others go on decoding."""
+    folder = model_folders(name, stored(dtype))
+    engine = engine_for(folder, dtype, max_tokens=8 * 64)
+    batches = {"A": [[5, 11, 17], [64, 3, 30], [1, 90, 65]],
+               "B": [[1, 7, 30, 64], [2, 100, 33, 5], [64, 65, 1, 128]],
+               "W": [[3, 75, 140], [71, 70, 69], [1, 200, 64]]}[name]
+    extra = [6, 2, 9, 4]                    # decode steps per request; unequal, so some end early
+    for b, lengths in enumerate(batches):
+        prompts = prompts_for(name, [n + e for n, e in zip(lengths, extra)], seed=10 + b)
+        want_all = [plain_logits(folder, p) for p in prompts]
+        slots = engine.open(len(prompts))
+        out = engine.step(slots, [p[:n] for p, n in zip(prompts, lengths)],
+                          [list(range(n)) for n in lengths]).cpu().numpy()
+        got = [[] for _ in prompts]
+        at = 0
+        for i, n in enumerate(lengths):
+            got[i].append(out[at:at + n])
+            at += n
+        live = list(range(len(prompts)))
+        fed = list(lengths)
+        while live:
+            out = engine.step([slots[i] for i in live],
+                              [prompts[i][fed[i]:fed[i] + 1] for i in live]).cpu().numpy()
+            for row, i in enumerate(live):
+                got[i].append(out[row:row + 1])
+                fed[i] += 1
+            done = [i for i in live if fed[i] == len(prompts[i])]
+            if done:
+                engine.close([slots[i] for i in done])     # shorter requests end earlier
+                live = [i for i in live if i not in done]
+            engine.cache.check()
+        for i, p in enumerate(prompts):
+            assert_close_to_plain(np.concatenate(got[i]), want_all[i], dtype,
+                                  f"{name} batch {b} request {i}")
+        assert engine.cache.slots.held == 0
+        assert all(g.pool.held == 0 for g in engine.cache.groups)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_batch_rows_equal_single_rows(dtype, engines):
+    """What else is in the batch changes nothing (to the bit in fp32)."""
+    engine = engines("B", dtype)
+    prompts = prompts_for("B", [9, 70, 1, 33], seed=3)
+    alone = [engine.forward(p) for p in prompts]
+    slots = engine.open(4)
+    out = engine.step(slots, prompts, [list(range(len(p))) for p in prompts]).cpu().numpy()
+    engine.close(slots)
+    at = 0
+    for p, a in zip(prompts, alone):
+        assert_same_logits(out[at:at + len(p)], a, dtype, f"len {len(p)} in a batch vs alone")
+        at += len(p)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_long_decoding(dtype, engines, model_folders):
+    engine = engines("W", dtype)
+    folder = model_folders("W", stored(dtype))
+    ids = prompts_for("W", [400], seed=4)[0]
+    (slot,) = engine.open(1)
+    rows = [engine.step([slot], [ids[:3]], [[0, 1, 2]]).cpu().numpy()]
+    for t in range(3, len(ids)):
+        rows.append(engine.step([slot], [ids[t:t + 1]]).cpu().numpy())
+    engine.close([slot])
+    assert_close_to_plain(np.concatenate(rows), plain_logits(folder, ids), dtype, "long decode")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_first_tokens_of_a_sequence(name, dtype, engines, model_folders):
+    engine = engines(name, dtype)
+    folder = model_folders(name, stored(dtype))
+    ids = prompts_for(name, [4], seed=6)[0]
+    (slot,) = engine.open(1)
+    rows = [engine.step([slot], [ids[t:t + 1]]).cpu().numpy() for t in range(4)]
+    engine.close([slot])
+    assert_close_to_plain(np.concatenate(rows), plain_logits(folder, ids), dtype, "first tokens")
+
+
+def test_greedy_generation_through_the_entry_point(engines, model_folders):
+    engine = engines("A", "float32")
+    config, tensors = plain.read_model_folder(model_folders("A", "float32"))
+    prompts = prompts_for("A", [5, 11, 17])
+    want = [plain.generate(config, tensors, p, 8) for p in prompts]
+    got = engine.generate([p.tolist() for p in prompts], 8, stop_at_eos=False)
+    assert [g.tolist() for g in got] == want
+    assert all(g.dtype == np.int32 for g in got)
+    one = engine.generate(prompts[1], 8, stop_at_eos=False)
+    assert one.tolist() == want[1] and engine.ending.state == "complete"
+    # a stop token ends a request early and is kept; the others go on
+    stop = want[0][2]
+    got = engine.generate([p.tolist() for p in prompts], 8, stop_token_ids=[stop])
+    for g, w, e in zip(got, want, engine.endings):
+        cut = w.index(stop) + 1 if stop in w else len(w)
+        assert g.tolist() == w[:cut]
+        assert e.reason == ("stop" if stop in w else "length")
+    assert engine.generate(prompts[0], 0).size == 0
+    assert engine.cache.slots.held == 0
+
+
+def test_temperature_generation_matches_the_plain_sampler(engines, model_folders):
+    engine = engines("B", "float32")
+    config, tensors = plain.read_model_folder(model_folders("B", "float32"))
+    prompts = prompts_for("B", [1, 7, 30, 64])
+    want = [plain.generate(config, tensors, p, 16, temperature=0.8, seed=1234, request=i)
+            for i, p in enumerate(prompts)]
+    got = engine.generate([p.tolist() for p in prompts], 16, stop_at_eos=False,
+                          temperature=0.8, seed=1234)
+    assert [g.tolist() for g in got] == want
+    greedy = engine.generate([p.tolist() for p in prompts], 16, stop_at_eos=False)
+    assert [g.tolist() for g in greedy] != want
+    # what a request draws does not depend on its batch: two batches of two
+    small = Engine_like(engine, max_batch=2)
+    again = small.generate([p.tolist() for p in prompts], 16, stop_at_eos=False,
+                           temperature=0.8, seed=1234)
+    assert [g.tolist() for g in again] == want
+
+
+def Engine_like(engine, **kw):
+    from semantic_aware_adaptive_kv_cache_precision_b200 import Engine
+    return Engine(engine.model_dir, dtype=engine.dtype, max_tokens=2048, **kw).load_weights()
+
+
+def test_generation_refuses_bad_requests(engines):
+    engine = engines("A", "float32")
+    with pytest.raises(ValueError, match="1-D"):
+        engine.generate(np.zeros((2, 3), dtype=np.int64), 4)
+    with pytest.raises(ValueError, match="empty"):
+        engine.generate([], 4)
+    with pytest.raises(ValueError, match=r"\[0, 512\)"):
+        engine.generate([1, 512], 4)
+    with pytest.raises(ValueError, match="context window"):
+        engine.generate([1] * 120, 20)
+    with pytest.raises(ValueError, match="negative"):
+        engine.generate([1], -1)
+    assert engine.cache is None or engine.cache.slots.held == 0
+
+
+def test_reports_and_endings(engines):
+    engine = engines("A", "float32")
+    seen = []
+    out = engine.generate([3, 4, 5], 4, stop_at_eos=False, report=lambda *a: seen.append(a))
+    assert seen[0] == ("prefilling", 3, None)
+    assert [s[0] for s in seen[1:]] == ["decoding"] * 3
+    assert [s[2] for s in seen[1:]] == out[1:].tolist()
+    assert [s[1] for s in seen[1:]] == [4, 5, 6]
+    assert engine.ending.positions == 6 and engine.ending.reason == "length"
+
+
+def test_cache_full_ends_requests_gracefully(model_folders):
+    engine = engine_for(model_folders("A", "float32"), "float32", max_tokens=64)
+    with pytest.raises(ValueError, match="cache holds"):
+        engine.generate([1] * 60, 20, stop_at_eos=False)
+    out = engine.generate([[1] * 30, [2] * 30], 5, stop_at_eos=False)     # one block: two batches
+    assert all(len(o) == 5 for o in out)
+    assert engine.cache.slots.held == 0
+    # a step that outgrows the cache takes nothing and leaves the sequence as it was
+    from semantic_aware_adaptive_kv_cache_precision_b200 import CacheFull
+    (slot,) = engine.open(1)
+    engine.step([slot], [[1] * 64])
+    with pytest.raises(CacheFull, match="nothing was taken"):
+        engine.step([slot], [[3]])
+    assert engine.cache.lengths[slot] == 64
+    engine.close([slot])
+    engine.cache.check()

@@ -1,0 +1,339 @@
+"""Each kernel alone against a plain float64 reference, at sizes other than the
+engine tests': widths and vocabularies that are no power of two, head sizes in
+steps of 16, odd numbers of heads and groups, scattered cache blocks."""
+
+import numpy as np
+import pytest
+import torch
+
+import plain_model as plain
+from semantic_aware_adaptive_kv_cache_precision_b200 import ops
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+ULP = {torch.float32: 2.0 ** -23, torch.bfloat16: 2.0 ** -8}
+
+
+def dev(a, dtype=torch.float32):
+    return torch.as_tensor(np.asarray(a)).to(DEV).to(dtype).contiguous()
+
+
+def host(t):
+    return t.detach().double().cpu().numpy()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_embed(dtype):
+    rng = np.random.default_rng(0)
+    table = dev(rng.standard_normal((301, 70)), dtype)
+    ids = torch.tensor([0, 300, 5, 301, -1, 17], dtype=torch.int32, device=DEV)
+    out = ops.embed(ids, table)
+    assert out.dtype == torch.float32
+    want = host(table)[[0, 300, 5, 0, 0, 17]]
+    want[3] = want[4] = 0.0                     # ids outside the table give zero rows
+    np.testing.assert_array_equal(host(out), want)
+
+
+@pytest.mark.parametrize("hidden", [48, 200, 1536, 5001])
+@pytest.mark.parametrize("wdtype,odtype", [(torch.float32, torch.float32),
+                                           (torch.bfloat16, torch.bfloat16),
+                                           (torch.float32, torch.bfloat16)])
+def test_rms_norm(hidden, wdtype, odtype):
+    rng = np.random.default_rng(hidden)
+    x = dev(rng.standard_normal((7, hidden)) * 3.0)
+    w = dev(1 + 0.1 * rng.standard_normal(hidden), wdtype)
+    eps = 1e-5
+    want = plain.rms_norm(host(x), host(w), eps)
+    got = ops.rms_norm(x, w, eps, odtype)
+    np.testing.assert_allclose(host(got), want, rtol=2 * ULP[odtype], atol=1e-30)
+    rows = torch.tensor([6, 0, 3], dtype=torch.int32, device=DEV)
+    picked = ops.rms_norm(x, w, eps, odtype, rows=rows)
+    assert torch.equal(picked, got[[6, 0, 3]])          # rows are independent, to the bit
+    # eps matters when the row is tiny
+    tiny = dev(np.full((1, hidden), 1e-4))
+    np.testing.assert_allclose(host(ops.rms_norm(tiny, w, 1e-2, torch.float32)),
+                               plain.rms_norm(host(tiny), host(w), 1e-2), rtol=1e-5)
+
+
+def make_cache(rng, n_blocks, kv_heads, head_dim, dtype):
+    k = dev(rng.standard_normal((n_blocks, kv_heads, ops.CACHE_BLOCK, head_dim)), dtype)
+    v = dev(rng.standard_normal((n_blocks, kv_heads, ops.CACHE_BLOCK, head_dim)), dtype)
+    return k, v
+
+
+def gather_cache(cache, table_row, length):
+    """[length, kv_heads, head_dim] float64 of one sequence from its blocks."""
+    c = host(cache)
+    rows = [c[table_row[p // 64], :, p % 64, :] for p in range(length)]
+    return np.stack(rows)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("heads,kv_heads,head_dim,rot", [(4, 2, 16, 16), (6, 3, 48, 32),
+                                                         (5, 1, 128, 128), (2, 2, 256, 64)])
+def test_rope_store(dtype, heads, kv_heads, head_dim, rot):
+    rng = np.random.default_rng(heads * head_dim)
+    starts, counts = [0, 130, 63], [70, 1, 3]           # three sequences, one in mid-decode
+    T = sum(counts)
+    width = (heads + 2 * kv_heads) * head_dim
+    qkv = dev(rng.standard_normal((T, width)), dtype)
+    before = host(qkv)
+    positions = np.concatenate([np.arange(s, s + c) for s, c in zip(starts, counts)])
+    token_seq = np.repeat(np.arange(3), counts)
+    table = np.array([[5, 2, -1, -1], [7, 0, 3, -1], [1, 6, -1, -1]], dtype=np.int32)
+    k_cache, v_cache = make_cache(rng, 8, kv_heads, head_dim, dtype)
+    k0, v0 = host(k_cache).copy(), host(v_cache).copy()
+    theta = 1e4
+    j = np.arange(rot // 2)
+    angle = np.arange(256)[:, None] * np.power(theta, -2.0 * j / rot)[None, :]
+    cos, sin = dev(np.cos(angle)), dev(np.sin(angle))
+    ops.rope_store(qkv, dev(positions, torch.int32), dev(token_seq, torch.int32),
+                   dev(table, torch.int32), cos, sin, k_cache, v_cache, heads, kv_heads, head_dim)
+    c, s = host(cos)[positions], host(sin)[positions]
+
+    def rotate(x):                                        # x [T, h, d]
+        out = x.copy()
+        out[..., :rot] = plain.rotate_half(x[..., :rot], c, s)
+        return out
+
+    q_want = rotate(before[:, :heads * head_dim].reshape(T, heads, head_dim))
+    k_want = rotate(before[:, heads * head_dim:(heads + kv_heads) * head_dim]
+                    .reshape(T, kv_heads, head_dim))
+    v_want = before[:, (heads + kv_heads) * head_dim:].reshape(T, kv_heads, head_dim)
+    tol = dict(rtol=0, atol=4 * ULP[dtype] * 4)
+    np.testing.assert_allclose(host(qkv)[:, :heads * head_dim].reshape(T, heads, head_dim),
+                               q_want, **tol)
+    np.testing.assert_array_equal(host(qkv)[:, heads * head_dim:], before[:, heads * head_dim:])
+    k1, v1 = host(k_cache), host(v_cache)
+    touched = np.zeros(k1.shape[:1] + k1.shape[2:3], dtype=bool)      # [block, offset]
+    for t in range(T):
+        b, o = table[token_seq[t], positions[t] // 64], positions[t] % 64
+        np.testing.assert_allclose(k1[b, :, o, :], k_want[t], **tol)
+        np.testing.assert_array_equal(v1[b, :, o, :], v_want[t])
+        touched[b, o] = True
+    # nothing else in the cache changed
+    untouched = ~touched
+    for now, was in ((k1, k0), (v1, v0)):
+        np.testing.assert_array_equal(now.transpose(0, 2, 1, 3)[untouched],
+                                      was.transpose(0, 2, 1, 3)[untouched])
+
+
+def attention_reference(q, k, v, pos, heads, kv_heads, scale, window):
+    """One query [heads, d] at position pos over keys [len, kv_heads, d]."""
+    out = np.empty_like(q)
+    first = max(0, pos - window + 1) if window else 0
+    for h in range(heads):
+        g = h // (heads // kv_heads)
+        s = (k[first:pos + 1, g] @ q[h]) * scale
+        p = np.exp(s - s.max())
+        out[h] = (p / p.sum()) @ v[first:pos + 1, g]
+    return out
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("heads,kv_heads,head_dim,window", [
+    (4, 2, 16, None), (6, 1, 32, None), (7, 7, 80, None), (12, 2, 128, 100), (3, 3, 256, 64),
+    (10, 5, 112, 1)])
+def test_attention_plain(dtype, heads, kv_heads, head_dim, window):
+    rng = np.random.default_rng(head_dim + heads)
+    # sequences: a 150-token prefill, a decode at position 299, a 2-token chunk after 64
+    starts, counts = [0, 299, 64], [150, 1, 2]
+    table = np.array([[9, 4, 11, -1, -1], [0, 8, 2, 6, 10], [3, 7, -1, -1, -1]], dtype=np.int32)
+    k_cache, v_cache = make_cache(rng, 12, kv_heads, head_dim, dtype)
+    T = sum(counts)
+    q = dev(rng.standard_normal((T, heads * head_dim)), dtype)
+    positions = np.concatenate([np.arange(s, s + c) for s, c in zip(starts, counts)])
+    token_seq = np.repeat(np.arange(3), counts)
+    scale = head_dim ** -0.5
+    got = ops.attention_plain(q, k_cache, v_cache, dev(positions, torch.int32),
+                              dev(token_seq, torch.int32), dev(table, torch.int32), heads,
+                              kv_heads, head_dim, scale, window)
+    qh = host(q).reshape(T, heads, head_dim)
+    for t in range(T):
+        s = token_seq[t]
+        length = positions[t] + 1
+        # blocks that fell out of a window may be gone (-1); they are never read
+        first = max(0, positions[t] - window + 1) if window else 0
+        kk = np.zeros((length, kv_heads, head_dim))
+        vv = np.zeros((length, kv_heads, head_dim))
+        kc, vc = host(k_cache), host(v_cache)
+        for p in range(first, length):
+            kk[p] = kc[table[s, p // 64], :, p % 64]
+            vv[p] = vc[table[s, p // 64], :, p % 64]
+        want = attention_reference(qh[t], kk, vv, positions[t], heads, kv_heads, scale, window)
+        np.testing.assert_allclose(host(got[t]).reshape(heads, head_dim), want, rtol=0,
+                                   atol=(2e-6 if dtype == torch.float32 else 8e-3),
+                                   err_msg=f"token {t} at position {positions[t]}")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_attention_finds_one_far_key_among_hundreds(dtype):
+    """Every key is noise but one, far back in another block, which the query
+    matches strongly: the output must be that key's value. A wrong block, a wrong
+    offset or a wrong KV head shows at once."""
+    rng = np.random.default_rng(5)
+    heads, kv_heads, d = 6, 3, 64
+    k_cache, v_cache = make_cache(rng, 10, kv_heads, d, dtype)
+    k_cache *= 0.1
+    table = np.array([[7, 1, 9, 3, 5, 0, 2, 8]], dtype=np.int32)
+    pos = 500
+    direction = rng.standard_normal(d)
+    direction /= np.linalg.norm(direction)
+    for far in (0, 63, 64, 257, 499, 500):
+        kc = k_cache.clone()
+        g = 1
+        kc[table[0, far // 64], g, far % 64] = dev(direction * 40.0, dtype)
+        q = np.zeros((1, heads, d))
+        q[0, 2] = direction * 40.0             # head 2 and 3 read KV head 1
+        q[0, 3] = direction * 40.0
+        got = ops.attention_plain(dev(q.reshape(1, -1), dtype), kc, v_cache,
+                                  dev([pos], torch.int32), dev([0], torch.int32),
+                                  dev(table, torch.int32), heads, kv_heads, d, d ** -0.5, None)
+        want = host(v_cache)[table[0, far // 64], g, far % 64]
+        for h in (2, 3):
+            np.testing.assert_allclose(host(got)[0, h * d:(h + 1) * d], want, rtol=0, atol=2e-2,
+                                       err_msg=f"far key at {far}, head {h}")
+        # a head of another group does not see it
+        other = host(got)[0, 0:d]
+        assert np.abs(other - want).max() > 0.1
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_attention_window_edge(dtype):
+    """A towering key exactly at the window's edge is seen; one position further
+    back it is not."""
+    rng = np.random.default_rng(6)
+    heads = kv_heads = 2
+    d, window, pos = 32, 70, 200
+    k_cache, v_cache = make_cache(rng, 4, kv_heads, d, dtype)
+    k_cache *= 0.1
+    table = np.array([[2, 0, 3, 1]], dtype=np.int32)
+    direction = np.ones(d) / np.sqrt(d)
+    q = np.tile(direction * 40.0, (1, heads))
+    for far, seen in ((pos - window + 1, True), (pos - window, False)):
+        kc = k_cache.clone()
+        kc[table[0, far // 64], :, far % 64] = dev(np.tile(direction * 40.0, (kv_heads, 1)), dtype)
+        got = ops.attention_plain(dev(q, dtype), kc, v_cache, dev([pos], torch.int32),
+                                  dev([0], torch.int32), dev(table, torch.int32), heads, kv_heads,
+                                  d, d ** -0.5, window)
+        want = host(v_cache)[table[0, far // 64], 0, far % 64]
+        close = np.abs(host(got)[0, :d] - want).max() < 2e-2
+        assert close == seen, f"key at {far} (window {window}, query at {pos})"
+
+
+def test_attention_ignores_what_lies_beyond_the_sequence():
+    """NaN in every cache place after the query's position, and in blocks of other
+    sequences, changes nothing."""
+    rng = np.random.default_rng(7)
+    heads, kv_heads, d = 4, 2, 16
+    k_cache, v_cache = make_cache(rng, 6, kv_heads, d, torch.float32)
+    table = np.array([[4, 1, -1]], dtype=np.int32)
+    q = dev(rng.standard_normal((1, heads * d)))
+    args = (dev([70], torch.int32), dev([0], torch.int32), dev(table, torch.int32), heads,
+            kv_heads, d, 0.25, None)
+    clean = ops.attention_plain(q, k_cache, v_cache, *args)
+    for c in (k_cache, v_cache):
+        c[1, :, 7:] = float("nan")              # positions 71.. of the sequence
+        c[[0, 2, 3, 5]] = float("nan")          # other sequences' blocks
+    dirty = ops.attention_plain(q, k_cache, v_cache, *args)
+    assert torch.equal(clean, dirty)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_gated_silu(dtype):
+    rng = np.random.default_rng(8)
+    gate = np.concatenate([rng.standard_normal((5, 171)) * 4, [[-100.0] * 171], [[90.0] * 171]])
+    up = rng.standard_normal((7, 171))
+    got = ops.gated_silu(dev(np.concatenate([gate, up], axis=1), dtype))
+    g, u = host(dev(gate, dtype)), host(dev(up, dtype))
+    want = g / (1 + np.exp(-g)) * u
+    np.testing.assert_allclose(host(got), want, rtol=2 * ULP[dtype], atol=1e-30)
+    assert np.isfinite(host(got)).all()
+    # gate and up are not interchangeable
+    swapped = ops.gated_silu(dev(np.concatenate([up, gate], axis=1), dtype))
+    assert not torch.equal(swapped, got)
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 70, 33), (17, 64, 16), (65, 130, 200), (3, 1000, 352),
+                                   (130, 48, 1)])
+def test_gemm_f32(M, N, K):
+    rng = np.random.default_rng(M * N + K)
+    x, w, b = rng.standard_normal((M, K)), rng.standard_normal((N, K)), rng.standard_normal(N)
+    xd, wd, bd = dev(x), dev(w), dev(b)
+    want = host(xd) @ host(wd).T
+    bound = 4 * np.sqrt(K) * 2.0 ** -24 * (np.abs(host(xd)) @ np.abs(host(wd)).T).max()
+    got = ops.linear(xd, wd)
+    assert np.abs(host(got) - want).max() <= bound
+    got_b = ops.linear(xd, wd, bd)
+    assert np.abs(host(got_b) - (want + host(bd))).max() <= bound + 1e-6
+    acc = dev(rng.standard_normal((M, N)))
+    before = host(acc)
+    assert ops.linear(xd, wd, accumulate_into=acc) is acc
+    assert np.abs(host(acc) - (before + want)).max() <= bound + 1e-6
+    # a row's result does not depend on which other rows are in the batch
+    for r in {0, M // 2, M - 1}:
+        alone = ops.linear(xd[r:r + 1], wd)
+        assert torch.equal(alone[0], got[r])
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 96, 64), (40, 200, 136), (300, 72, 1000)])
+def test_linear_bf16(M, N, K):
+    rng = np.random.default_rng(M + N + K)
+    xd, wd = dev(rng.standard_normal((M, K)), torch.bfloat16), dev(rng.standard_normal((N, K)),
+                                                                  torch.bfloat16)
+    bd = dev(rng.standard_normal(N), torch.bfloat16)
+    want = host(xd) @ host(wd).T
+    scale = np.abs(want).max()
+    got32 = ops.linear(xd, wd, out_dtype=torch.float32)
+    assert got32.dtype == torch.float32
+    assert np.abs(host(got32) - want).max() <= 1e-5 * scale * np.sqrt(K)
+    got = ops.linear(xd, wd, bd)
+    assert got.dtype == torch.bfloat16
+    assert np.abs(host(got) - (want + host(bd))).max() <= 2.0 ** -8 * (scale + 4)
+    acc = dev(rng.standard_normal((M, N)))
+    before = host(acc)
+    ops.linear(xd, wd, accumulate_into=acc)
+    assert np.abs(host(acc) - (before + want)).max() <= 1e-5 * scale * np.sqrt(K) + 1e-6
+
+
+def test_choose_greedy_rules():
+    rows = np.array([[1.0, 3.0, 3.0, 2.0], [np.nan, 0.5, np.nan, 0.1],
+                     [np.nan, np.nan, np.nan, np.nan], [-np.inf, -np.inf, -5.0, -np.inf]])
+    got = ops.choose(dev(rows)).cpu().tolist()
+    assert got == [1, 1, 4, 2]                  # 4 = past the end: no winner
+    rng = np.random.default_rng(9)
+    big = rng.standard_normal((5, 151937)).astype(np.float32)
+    big[2, 77] = big[2, 150000] = 9.0           # a tie far apart: the lower index
+    got = ops.choose(dev(big)).cpu().tolist()
+    assert got == [plain.greedy(r) for r in big] and got[2] == 77
+
+
+def test_choose_temperature_matches_plain_sampler():
+    rng = np.random.default_rng(10)
+    logits = (rng.standard_normal((6, 1000)) * 2).astype(np.float32)
+    request = np.array([0, 1, 2, 3, 40, 7], dtype=np.int32)
+    step = np.array([0, 5, 1, 1000, 3, 3], dtype=np.int32)
+    got = ops.choose(dev(logits), 0.7, 99, dev(request, torch.int32), dev(step, torch.int32))
+    want = [plain.sample(logits[i], 0.7, 99, int(request[i]), int(step[i])) for i in range(6)]
+    assert got.cpu().tolist() == want
+    # the row's place in the batch does not matter
+    again = ops.choose(dev(logits[[4]]), 0.7, 99, dev(request[[4]], torch.int32),
+                       dev(step[[4]], torch.int32))
+    assert again.cpu().tolist() == [want[4]]
+
+
+def test_kernels_refuse_what_they_cannot_take():
+    with pytest.raises(ops.KernelError, match="CUDA device only"):
+        ops.embed(torch.zeros(3, dtype=torch.int32), torch.zeros(4, 4))
+    x = torch.zeros((2, 8), device=DEV)
+    with pytest.raises(ops.KernelError):
+        ops.rms_norm(x, torch.zeros(9, device=DEV), 1e-6, torch.float32)
+    with pytest.raises(ops.KernelError, match="float32 or bfloat16"):
+        ops.gated_silu(torch.zeros((2, 8), device=DEV, dtype=torch.float16))
+    with pytest.raises(ops.KernelError, match="256"):
+        ops.attention_plain(torch.zeros((1, 512), device=DEV),
+                            torch.zeros((1, 1, 64, 512), device=DEV),
+                            torch.zeros((1, 1, 64, 512), device=DEV),
+                            torch.zeros(1, dtype=torch.int32, device=DEV),
+                            torch.zeros(1, dtype=torch.int32, device=DEV),
+                            torch.zeros((1, 1), dtype=torch.int32, device=DEV), 1, 1, 512, 1.0, None)
