@@ -1,0 +1,203 @@
+"""A toy architecture defined here, outside the package: a mixer with running
+state of its own (fixed size per sequence), used beside the package's attention
+in one model, with a layer that runs twice and a layer that reads another
+layer's cache. It is registered, written as a random checkpoint, loaded, and
+stepped whole, token by token and in unequal batches, without any change to the
+package's files, and compared with a plain NumPy version written below."""
+
+import json
+from dataclasses import dataclass
+
+import numpy as np
+import pytest
+import torch
+
+import plain_model as plain
+import semantic_aware_adaptive_kv_cache_precision_b200 as sakv
+from semantic_aware_adaptive_kv_cache_precision_b200.cache import StateNeed
+from semantic_aware_adaptive_kv_cache_precision_b200.config import (AttentionSpec, BlockSpec,
+                                                                     GatedMLPSpec, LayerCall,
+                                                                     ModelSpec, NormSpec,
+                                                                     RotarySpec)
+from semantic_aware_adaptive_kv_cache_precision_b200.parts import Part, register_part
+from semantic_aware_adaptive_kv_cache_precision_b200.weights import TensorDecl
+from helpers import assert_same_logits
+
+pytestmark = pytest.mark.gpu
+
+
+# ---- the toy mixer: s_t = decay * s_{t-1} + W_in h_t ;  out_t = W_out s_t -----------------
+
+@dataclass(frozen=True)
+class RunningStateSpec:
+    hidden: int
+    state: int
+    decay: float
+    kind: str = "toy_running_state"
+
+
+class RunningStateMixer(Part):
+    def tensor_decls(self):
+        s = self.spec
+        return [TensorDecl(self.prefix + "in_proj.weight", (s.state, s.hidden)),
+                TensorDecl(self.prefix + "out_proj.weight", (s.hidden, s.state))]
+
+    def bind(self, arena):
+        self.w_in = arena.view(self.prefix + "in_proj.weight")
+        self.w_out = arena.view(self.prefix + "out_proj.weight")
+
+    def cache_need(self):
+        return StateNeed((self.spec.state,), "float32")
+
+    def forward(self, h, step, view, residual, write_cache=True):
+        u = h.float() @ self.w_in.float().t()
+        out = torch.empty_like(u)
+        at = 0
+        for slot, count in zip(step.host_slots, step.new_counts):
+            s = view.state[slot].clone()
+            for t in range(at, at + count):
+                s = self.spec.decay * s + u[t]
+                out[t] = s
+            view.state[slot] = s
+            at += count
+        residual += out @ self.w_out.float().t()
+
+
+register_part("toy_running_state", RunningStateMixer)
+
+
+# ---- the toy architecture -------------------------------------------------------------------
+
+@dataclass(frozen=True)
+class ToyConfig:
+    hidden_size: int = 48
+    state_size: int = 20
+    decay: float = 0.8
+    num_attention_heads: int = 3
+    num_key_value_heads: int = 1
+    intermediate_size: int = 72
+    vocab_size: int = 211
+    rms_norm_eps: float = 1e-5
+    rope_theta: float = 3000.0
+    max_position_embeddings: int = 256
+
+    @classmethod
+    def from_dict(cls, raw):
+        return cls(**{k: raw[k] for k in cls.__dataclass_fields__ if k in raw})
+
+    def to_dict(self):
+        return {**self.__dict__, "architectures": ["ToyMixedForTests"]}
+
+    def model_spec(self):
+        h, d = self.hidden_size, self.hidden_size // self.num_attention_heads
+        norm = NormSpec(h, self.rms_norm_eps)
+        mlp = GatedMLPSpec(h, self.intermediate_size, "silu")
+        rotary = RotarySpec(d, d, self.rope_theta, self.max_position_embeddings)
+        attn = AttentionSpec(hidden=h, heads=self.num_attention_heads,
+                             kv_heads=self.num_key_value_heads, head_dim=d, qkv_bias=True,
+                             out_bias=False, scale=d ** -0.5, window=None, position=rotary)
+        blocks = (BlockSpec("model.layers.0.", RunningStateSpec(h, self.state_size, self.decay),
+                            norm, mlp, norm, mixer_name="mixer"),
+                  BlockSpec("model.layers.1.", attn, norm, mlp, norm),
+                  BlockSpec("model.layers.2.", attn, norm, mlp, norm))
+        # block 0 runs twice (two states); block 2 reads the cache that block 1 wrote
+        order = (LayerCall(0, 0), LayerCall(1, 1), LayerCall(0, 2), LayerCall(2, 1))
+        return ModelSpec(architecture="ToyMixedForTests", vocab_size=self.vocab_size, hidden=h,
+                         blocks=blocks, run_order=order, final_norm=norm, tie_head=True,
+                         max_positions=self.max_position_embeddings, stored_dtype="float32")
+
+
+sakv.register_architecture("ToyMixedForTests", ToyConfig)
+
+
+# ---- its plain version ------------------------------------------------------------------------
+
+def plain_toy(config: ToyConfig, t: dict, ids) -> np.ndarray:
+    n = len(ids)
+    heads, kvh = config.num_attention_heads, config.num_key_value_heads
+    d = config.hidden_size // heads
+    cos, sin = plain.rope_angles(np.arange(n), d, config.rope_theta)
+    eps = config.rms_norm_eps
+
+    def mlp(x, p):
+        w = {k[len(p + "mlp."):]: v for k, v in t.items() if k.startswith(p + "mlp.")}
+        return x + plain.swiglu_mlp(plain.rms_norm(x, t[p + "post_attention_layernorm.weight"], eps), w)
+
+    def state_layer(x):
+        p = "model.layers.0."
+        h = plain.rms_norm(x, t[p + "input_layernorm.weight"], eps)
+        u = h @ t[p + "mixer.in_proj.weight"].T
+        s, out = np.zeros(config.state_size), np.empty_like(u)
+        for i in range(n):
+            s = config.decay * s + u[i]
+            out[i] = s
+        return mlp(x + out @ t[p + "mixer.out_proj.weight"].T, p)
+
+    def attn_layer(x, p, kv=None):
+        h = plain.rms_norm(x, t[p + "input_layernorm.weight"], eps)
+        a = p + "self_attn."
+        q = plain.rotate_half(plain.linear(h, t[a + "q_proj.weight"], t[a + "q_proj.bias"])
+                              .reshape(n, heads, d), cos, sin)
+        if kv is None:
+            k = plain.rotate_half(plain.linear(h, t[a + "k_proj.weight"], t[a + "k_proj.bias"])
+                                  .reshape(n, kvh, d), cos, sin)
+            v = plain.linear(h, t[a + "v_proj.weight"], t[a + "v_proj.bias"]).reshape(n, kvh, d)
+            kv = (k, v)
+        k, v = kv
+        out = np.empty((n, heads, d))
+        for hd in range(heads):
+            g = hd // (heads // kvh)
+            s = np.where(plain.causal_mask(n), q[:, hd] @ k[:, g].T / np.sqrt(d), -np.inf)
+            out[:, hd] = plain.softmax(s) @ v[:, g]
+        x = x + out.reshape(n, -1) @ t[a + "o_proj.weight"].T
+        return mlp(x, p), kv
+
+    x = plain.embed(t["model.embed_tokens.weight"], ids)
+    x = state_layer(x)
+    x, kv = attn_layer(x, "model.layers.1.")
+    x = state_layer(x)
+    x, _ = attn_layer(x, "model.layers.2.", kv)
+    return plain.rms_norm(x, t["model.norm.weight"], eps) @ t["model.embed_tokens.weight"].T
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_architecture_registers_builds_and_steps(dtype, tmp_path):
+    config = ToyConfig()
+    folder = sakv.write_random_model(tmp_path / "toy", config, seed=3)
+    assert json.loads((folder / "config.json").read_text())["architectures"] == ["ToyMixedForTests"]
+    engine = sakv.Engine(folder, dtype=dtype, max_tokens=1024, poison_freed=True).load_weights()
+    needs = engine.model.cache_needs()
+    assert [type(n).__name__ for n in needs] == ["StateNeed", "KVNeed", "StateNeed"]
+    _, tensors = plain.read_model_folder(folder)
+    rng = np.random.default_rng(0)
+    prompts = [rng.integers(0, config.vocab_size, n) for n in (70, 9, 131)]
+    want = [plain_toy(config, tensors, p) for p in prompts]
+    tol = 2e-5 if dtype == "float32" else 0.06
+    whole = [engine.forward(p) for p in prompts]
+    for g, w in zip(whole, want):
+        scale = np.abs(w).max() if dtype == "float32" else w.std()
+        assert np.abs(g - w).max() <= tol * scale
+    # token by token: the running state is carried in the slot
+    (slot,) = engine.open(1)
+    rows = [engine.step([slot], [prompts[1][i:i + 1]]).cpu().numpy() for i in range(9)]
+    engine.close([slot])
+    assert np.abs(np.concatenate(rows) - whole[1]).max() <= tol * np.abs(whole[1]).max()
+    # an unequal batch, twice in a row, so that slots (and their state) are used again
+    for _ in range(2):
+        slots = engine.open(3)
+        heads = [len(p) - 4 for p in prompts]
+        out = engine.step(slots, [p[:h] for p, h in zip(prompts, heads)],
+                          [list(range(h)) for h in heads]).cpu().numpy()
+        rows = [[out[sum(heads[:i]):sum(heads[:i + 1])]] for i in range(3)]
+        for t in range(4):
+            out = engine.step(slots, [p[h + t:h + t + 1] for p, h in zip(prompts, heads)])
+            for i in range(3):
+                rows[i].append(out[i:i + 1].cpu().numpy())
+        engine.close(slots)
+        for i in range(3):
+            got = np.concatenate(rows[i])
+            scale = np.abs(want[i]).max() if dtype == "float32" else want[i].std()
+            assert np.abs(got - want[i]).max() <= tol * scale, f"request {i}"
+    engine.cache.check()
+    out = engine.generate([p.tolist() for p in prompts[:2]], 5, stop_at_eos=False)
+    assert [len(o) for o in out] == [5, 5]
