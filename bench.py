@@ -1,0 +1,298 @@
+#!/usr/bin/env python3
+"""Decode and prefill throughput of the engine on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+The default run has the layer sizes of Qwen2.5-1.5B (28 layers, hidden 1536, 12
+heads, 2 KV heads, head size 128, intermediate 8960, vocabulary 151936, tied
+head) with random weights in bfloat16, a batch of 8 sequences that each hold
+2,048 cached tokens, and times K decode steps (one new token per sequence a
+step) on the device with CUDA events. It prints ONE JSON line:
+
+* `value`: decoded tokens a second (batch x K / time), kernels and cache of the
+  engine, tokens chosen on the device and read back every step;
+* `e2e`: the same through `Engine.generate` with host token lists in and out
+  (time of K+1 new tokens minus time of 1 new token, as the reference's
+  `tools/throughput.py:66-73` measures decoding);
+* `prefill`: one 2,048-token prompt in one step, with the fraction of the
+  measured bf16 peak that its flops reach;
+* `roofline`: the decode step's bytes (every weight once, plus the cache of the
+  live sequences) over its time, against the measured copy bandwidth;
+* `points`: decoding at batch 1 and 64.
+
+This library runs on one GPU; for --gpus > 1 it says so and exits with 2.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+QWEN25_1P5B = {
+    "architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2",
+    "num_hidden_layers": 28, "hidden_size": 1536, "num_attention_heads": 12,
+    "num_key_value_heads": 2, "intermediate_size": 8960, "vocab_size": 151936,
+    "max_position_embeddings": 32768, "rope_theta": 1000000.0, "rms_norm_eps": 1e-6,
+    "tie_word_embeddings": True, "hidden_act": "silu", "torch_dtype": "bfloat16",
+    "use_sliding_window": False, "eos_token_id": 151645,
+}
+CONTEXT = 2048
+PREFILL_TOKENS = 2048
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+def peaks() -> dict:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        try:
+            raw = json.load(open(path))
+            out = {"hbm_gbs": float(raw["hbm_gbs"]), "bf16_tflops": float(raw["bf16_tflops"]),
+                   "source": "measured"}
+            if "bf16_tflops_sustained" in raw:
+                out["bf16_tflops_sustained"] = float(raw["bf16_tflops_sustained"])
+            return out
+        except (KeyError, ValueError, TypeError):
+            pass
+    return dict(FALLBACK_PEAKS)
+
+
+class ClockSampler:
+    """nvidia-smi in the background, sampling SM clocks and throttle reasons."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        clocks, top, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) != 6:
+                continue
+            try:
+                clocks.append(float(parts[0]))
+                top = float(parts[1])
+            except ValueError:
+                continue
+            for name, flag in zip(names, parts[2:]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(clocks) if clocks else None, "sm_max_mhz": top,
+                "reasons": sorted(reasons), "samples": len(clocks)}
+
+
+def decode_bytes(cfg, batch: int, context: int) -> int:
+    """Bytes a decode step has to read: every weight it uses once (all layers, the
+    norms, the output head; of the embedding only the batch's rows) and the
+    cached keys and values of the live sequences."""
+    H, A, G, I, V, L = (cfg.hidden_size, cfg.num_attention_heads, cfg.num_key_value_heads,
+                        cfg.intermediate_size, cfg.vocab_size, cfg.num_hidden_layers)
+    d = cfg.head_dim
+    per_layer = (A + 2 * G) * d * H + (A + 2 * G) * d + A * d * H + 3 * H * I + 2 * H
+    weights = 2 * (L * per_layer + H + V * H + batch * H)
+    cache = batch * context * L * 2 * G * d * 2
+    return weights + cache
+
+
+def prefill_flops(cfg, tokens: int) -> float:
+    H, A, G, I, V, L = (cfg.hidden_size, cfg.num_attention_heads, cfg.num_key_value_heads,
+                        cfg.intermediate_size, cfg.vocab_size, cfg.num_hidden_layers)
+    d = cfg.head_dim
+    linear = 2.0 * tokens * ((A + 2 * G) * d * H + A * d * H + 3 * H * I)
+    attention = 4.0 * A * d * tokens * (tokens + 1) / 2
+    return L * (linear + attention) + 2.0 * H * V
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--layers", type=int, default=None,
+                    help="fewer layers than the configuration has (recorded in config)")
+    ap.add_argument("--no-points", action="store_true", help="skip batch 1 and 64")
+    ap.add_argument("--no-e2e", action="store_true")
+    args = ap.parse_args()
+
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "the reference builds a pybind11/CUDA extension for the local GPU with "
+                          "scikit-build-core and needs the `tokenizers` wheel and real checkpoints; "
+                          "it has no random-weights mode and no batch dimension, so it cannot run "
+                          "this metric offline"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py: this library runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    if args.warmup < 3:
+        args.warmup = 3
+
+    import numpy as np
+    import torch
+    import semantic_aware_adaptive_kv_cache_precision_b200 as sakv
+    from semantic_aware_adaptive_kv_cache_precision_b200 import sampling
+    from semantic_aware_adaptive_kv_cache_precision_b200.ops import _lib
+
+    raw = dict(QWEN25_1P5B)
+    full_layers = raw["num_hidden_layers"]
+    if args.layers:
+        raw["num_hidden_layers"] = args.layers
+    cfg = sakv.config_from_dict(raw)
+    K, W = args.steps, args.warmup
+    batches = [args.batch] + ([] if args.no_points else [b for b in (1, 64) if b != args.batch])
+    most = max(batches)
+    room = -(-(CONTEXT + K + W + 8) // 64) * 64
+    engine = sakv.Engine(config=cfg, dtype="bfloat16", random_seed=0, max_batch=most,
+                         max_tokens=most * room, max_step_tokens=8192).load_weights()
+    pk = peaks()
+    rng = np.random.default_rng(0)
+    greedy = sampling.SamplingParams()
+
+    def filled(batch: int):
+        """`batch` sequences that each hold CONTEXT cached tokens (a real prefill)."""
+        slots = engine.open(batch)
+        for begin in range(0, batch, 4):
+            part = slots[begin:begin + 4]
+            engine.step(part, [rng.integers(0, cfg.vocab_size, CONTEXT) for _ in part],
+                        [[] for _ in part])
+        return slots
+
+    def decode_run(batch: int, steps: int, warmup: int):
+        slots = filled(batch)
+        tokens = [rng.integers(0, cfg.vocab_size, 1) for _ in slots]
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+        def one():
+            logits = engine.step(slots, tokens)
+            chosen = sampling.choose(logits, greedy).cpu().numpy()
+            return [chosen[i:i + 1] for i in range(batch)]
+
+        for _ in range(warmup):
+            tokens = one()
+        torch.cuda.synchronize()
+        launches0 = _lib.launches
+        sampler = ClockSampler()
+        sampler.start()
+        start.record()
+        for _ in range(steps):
+            tokens = one()
+        stop.record()
+        torch.cuda.synchronize()
+        clocks = sampler.stop()
+        ms = start.elapsed_time(stop)
+        engine.close(slots)
+        return ms, _lib.launches - launches0, clocks
+
+    # -- the headline: decode at the default batch ------------------------------------
+    ms, launches, clocks = decode_run(args.batch, K, W)
+    ms_per_step = ms / K
+    value = args.batch * K / (ms / 1e3)
+    mid_context = CONTEXT + W + K // 2
+    achieved = decode_bytes(cfg, args.batch, mid_context) / (ms_per_step / 1e3) / 1e9
+
+    points = {}
+    for b in batches[1:]:
+        steps_b = max(16, min(K, 64))
+        ms_b, _, _ = decode_run(b, steps_b, W)
+        points[f"decode_b{b}"] = round(b * steps_b / (ms_b / 1e3), 1)
+    points[f"decode_b{args.batch}"] = round(value, 1)
+
+    # -- prefill of one 2,048-token prompt ----------------------------------------------
+    prompt = rng.integers(0, cfg.vocab_size, PREFILL_TOKENS)
+    times = []
+    for i in range(W + 5):
+        (slot,) = engine.open(1)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        sampling.choose(engine.step([slot], [prompt]), greedy)
+        b.record()
+        torch.cuda.synchronize()
+        engine.close([slot])
+        if i >= W:
+            times.append(a.elapsed_time(b))
+    prefill_ms = statistics.median(times)
+    peak_tflops = pk.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"])
+    prefill = {"value": round(PREFILL_TOKENS / (prefill_ms / 1e3), 1), "tokens": PREFILL_TOKENS,
+               "ms": round(prefill_ms, 3),
+               "frac": round(prefill_flops(cfg, PREFILL_TOKENS) / (prefill_ms / 1e3) / 1e12
+                             / peak_tflops, 4)}
+
+    # -- end to end through Engine.generate: host tokens in, host tokens out ----------------
+    e2e = None
+    if not args.no_e2e:
+        prompts = [rng.integers(0, cfg.vocab_size, CONTEXT).tolist() for _ in range(args.batch)]
+
+        def timed(new_tokens: int) -> float:
+            torch.cuda.synchronize()
+            began = time.perf_counter()
+            out = engine.generate(prompts, new_tokens, stop_at_eos=False)
+            assert all(len(o) == new_tokens for o in out)
+            return time.perf_counter() - began
+
+        timed(2)
+        short = statistics.median(timed(1) for _ in range(3))
+        long = statistics.median(timed(K + 1) for _ in range(3))
+        step_s = max(long - short, 1e-9) / K
+        e2e = {"value": round(args.batch / step_s, 1), "unit": "tokens/s",
+               "h2d_bytes_per_step": engine._stager.last_bytes,
+               "d2h_bytes_per_step": 4 * args.batch, "ms_per_step": round(step_s * 1e3, 4)}
+
+    line = {
+        "metric": "decode tokens/s (Qwen2.5-1.5B shape, batch 8, 2048 cached tokens)",
+        "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W,
+        "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic: random weights, random token ids",
+        "impl": "ours",
+        "config": {"model": "Qwen2.5-1.5B shape", "layers": cfg.num_hidden_layers,
+                   "layers_of_model": full_layers, "hidden": cfg.hidden_size,
+                   "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
+                   "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size,
+                   "vocab": cfg.vocab_size, "tied_head": cfg.tie_word_embeddings,
+                   "global_batch": args.batch, "seq_len": CONTEXT, "new_tokens": K,
+                   "parallelism": "single GPU", "l2": "weights (3.1 GB) exceed L2; no flush",
+                   "peaks": pk["source"]},
+        "prefill": prefill,
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"],
+                     "unit": "GB/s", "frac": round(achieved / pk["hbm_gbs"], 4)},
+        "points": points,
+        "clocks": clocks,
+        "gpu_launches": launches,
+    }
+    if e2e is not None:
+        line["e2e"] = e2e
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

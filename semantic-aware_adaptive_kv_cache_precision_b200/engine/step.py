@@ -50,6 +50,7 @@ class StepStager:
         self.capacity = 0
         self.host = self.dev = None
         self.copied = None
+        self.last_bytes = 0
 
     def _ensure(self, count: int) -> None:
         if count <= self.capacity:
@@ -97,6 +98,7 @@ class StepStager:
         put("want", want_rows)
         for g, t in enumerate(tables):
             put(f"table{g}", t)
+        self.last_bytes = 4 * total
         self.dev[:total].copy_(self.host[:total], non_blocking=True)
         self.copied = torch.cuda.Event()
         self.copied.record()

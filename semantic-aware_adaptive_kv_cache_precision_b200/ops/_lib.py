@@ -69,7 +69,13 @@ def require_cuda(*tensors) -> None:
                               f"{t.device}; there is no CPU implementation")
 
 
+#: kernels of this library launched by this process (benchmarks report the count)
+launches = 0
+
+
 def call(name: str, *args) -> None:
+    global launches
+    launches += 1
     code = function(name)(*args, stream())
     if code != 0:
         raise KernelError(f"{name} failed with CUDA error {code}"

@@ -76,6 +76,7 @@ def random_arena(decls: list[TensorDecl], seed: int, std: float, mode: str, devi
     but the device's own random stream."""
     from .loader import device_dtype
     code = {"bfloat16": "BF16", "float16": "F16", "float32": "F32"}[stored]
+    stored_dtype = _TORCH[stored]
     dtypes = {d.name: device_dtype("I32" if d.integer else code, mode) for d in decls}
     arena = WeightArena(decls, dtypes, device)
     gen = torch.Generator(device=device)
@@ -96,5 +97,5 @@ def random_arena(decls: list[TensorDecl], seed: int, std: float, mode: str, devi
                                     dtype=torch.float32) * std
                 if d.init == "ones_normal":
                     noise += 1.0
-                part.copy_(noise)
+                part.copy_(noise.to(stored_dtype))     # the value a checkpoint would store
     return arena
