@@ -1,0 +1,353 @@
+// Decode attention in bfloat16: one new token per sequence attends over its cached
+// keys and values, split along the keys (flash-decoding) so that a small batch
+// still fills the GPU, with a second kernel that folds the splits together.
+//
+//   grid  = (splits, kv_heads, sequences); block = 4 compute warps + 1 copy warp
+//   tile  = one cache block: 64 keys x head_dim, fetched by TMA (128-byte swizzle)
+//           into a ring of shared-memory stages guarded by full/empty mbarriers
+//   warp w of a block takes keys 16w..16w+15 of every tile for ALL query heads of
+//   the KV head's group (rows of an m16n8k16 tensor-core product), keeps its own
+//   running maximum, sum and output, and the four warps are merged at the end.
+//
+// Scores, maximum, exp2, sums and the output accumulate in fp32; probabilities
+// are rounded to bf16 for the P.V product, as keys and values are stored. The
+// reference's decode shape is one block per KV group with split runs of keys
+// folded by `combine_kernel` (`src/core_kernels/attention.cu:754-815, 878-950`).
+#include "common.cuh"
+#include "mma.cuh"
+#include "tma.cuh"
+
+namespace {
+
+constexpr int KT = kCacheBlock;      // keys per tile
+constexpr int kComputeWarps = 4;
+constexpr int kThreads = (kComputeWarps + 1) * 32;
+constexpr int kStages = 3;
+
+template <int D>
+struct Smem {
+  static constexpr int kBoxes = D / 64;               // 64-wide boxes per row of head_dim
+  static constexpr int kTileBytes = KT * D * 2;       // one K or V tile
+  static constexpr int kStageBytes = 2 * kTileBytes;  // K then V
+  static constexpr int kBytes = kStages * kStageBytes + 1024 /* alignment */ + 256;
+};
+
+template <int D>
+__global__ void __launch_bounds__(kThreads)
+decode_attention_kernel(const __grid_constant__ CUtensorMap k_map,
+                        const __grid_constant__ CUtensorMap v_map,
+                        const __nv_bfloat16* __restrict__ q, long long q_stride,
+                        const int32_t* __restrict__ seq_lens,
+                        const int32_t* __restrict__ block_table, int max_blocks,
+                        __nv_bfloat16* __restrict__ out, float* __restrict__ part_o,
+                        float* __restrict__ part_ml, int heads, int kv_heads, int splits,
+                        float scale_log2e, int window, int* __restrict__ error) {
+  using S = Smem<D>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~uintptr_t(1023));
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + kStages * S::kStageBytes);
+  uint64_t* empty = full + kStages;
+
+  const int split = blockIdx.x, g = blockIdx.y, b = blockIdx.z;
+  const int group = heads / kv_heads;       // query heads per KV head (<= 16 here)
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  const int kv_len = seq_lens[b];
+  const int first_key = (window > 0 && kv_len - window > 0) ? kv_len - window : 0;
+  const int first_tile = first_key / KT;
+  const int n_tiles = (kv_len + KT - 1) / KT;
+  const int count = n_tiles - first_tile;
+  const int per_split = (count + splits - 1) / splits;
+  const int t0 = first_tile + split * per_split;
+  const int t1 = min(n_tiles, t0 + per_split);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      tma::mbar_init(&full[s], 1);
+      tma::mbar_init(&empty[s], kComputeWarps);
+    }
+    tma::fence_barrier_init();
+  }
+  __syncthreads();
+
+  if (warp == kComputeWarps) {
+    // ---- the copy warp: one lane feeds the ring ---------------------------------
+    if (lane == 0) {
+      tma::prefetch_map(&k_map);
+      tma::prefetch_map(&v_map);
+      for (int t = t0, i = 0; t < t1; ++t, ++i) {
+        const int stage = i % kStages;
+        if (i >= kStages &&
+            !tma::mbar_wait(&empty[stage], ((i / kStages) - 1) & 1, error, 101))
+          break;
+        const int block = block_table[(long long)b * max_blocks + t];
+        const int row0 = (block * kv_heads + g) * KT;
+        uint8_t* dst = smem + stage * S::kStageBytes;
+        tma::mbar_expect_tx(&full[stage], S::kStageBytes);
+        for (int x = 0; x < S::kBoxes; ++x) {
+          tma::load_2d(dst + x * (KT * 128), &k_map, x * 64, row0, &full[stage]);
+          tma::load_2d(dst + S::kTileBytes + x * (KT * 128), &v_map, x * 64, row0, &full[stage]);
+        }
+      }
+    }
+    return;
+  }
+
+  // ---- compute warps ------------------------------------------------------------
+  // Query rows of this warp's m16 tile: row r = head g*group + r, rows >= group are zero.
+  uint32_t qf[D / 16][4];
+  {
+    const int r0 = lane >> 2, r1 = r0 + 8, c = (lane & 3) * 2;
+    const __nv_bfloat16* qb = q + (long long)b * q_stride + (long long)g * group * D;
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) {
+      const int col = ks * 16 + c;
+      qf[ks][0] = r0 < group ? *reinterpret_cast<const uint32_t*>(qb + r0 * D + col) : 0u;
+      qf[ks][1] = r1 < group ? *reinterpret_cast<const uint32_t*>(qb + r1 * D + col) : 0u;
+      qf[ks][2] = r0 < group ? *reinterpret_cast<const uint32_t*>(qb + r0 * D + col + 8) : 0u;
+      qf[ks][3] = r1 < group ? *reinterpret_cast<const uint32_t*>(qb + r1 * D + col + 8) : 0u;
+    }
+  }
+  float o[D / 8][4];
+#pragma unroll
+  for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  bool alive = true;
+
+  for (int t = t0, i = 0; t < t1; ++t, ++i) {
+    const int stage = i % kStages;
+    if (!tma::mbar_wait(&full[stage], (i / kStages) & 1, error, 102)) {
+      alive = false;
+      break;
+    }
+    const uint32_t kbase = tma::smem_u32(smem + stage * S::kStageBytes);
+    const uint32_t vbase = kbase + S::kTileBytes;
+    const int key0 = t * KT + warp * 16;            // this warp's first key of the tile
+    const int valid = kv_len - key0;                 // keys of this warp that exist
+    if (valid < 16) {
+      // Rows past the sequence's end hold whatever the block held before: zero this
+      // warp's own value rows there, so that 0 * garbage cannot become NaN.
+      uint8_t* vt = smem + stage * S::kStageBytes + S::kTileBytes;
+      for (int r = max(valid, 0); r < 16; ++r)
+        for (int x = 0; x < S::kBoxes; ++x)
+          reinterpret_cast<uint32_t*>(vt + x * (KT * 128) + (warp * 16 + r) * 128)[lane] = 0u;
+      __syncwarp();
+    }
+    // S = Q K^T for 16 keys: two n-tiles of 8 keys
+    float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+    {
+      const int row = warp * 16 + (lane & 7) + ((lane >> 4) << 3);   // key row this lane addresses
+      const int half = (lane >> 3) & 1;                              // dims 0-7 or 8-15 of the k-step
+#pragma unroll
+      for (int ks = 0; ks < D / 16; ++ks) {
+        const int chunk = ks * 2 + half;                             // 16-byte chunk along head_dim
+        uint32_t b0, b1, b2, b3;
+        mma::ldmatrix_x4(mma::swizzled(kbase + (chunk >> 3) * (KT * 128), row, chunk & 7), b0, b1,
+                         b2, b3);
+        mma::bf16_16816(s[0], qf[ks], b0, b1);
+        mma::bf16_16816(s[1], qf[ks], b2, b3);
+      }
+    }
+    // scale, mask, running maximum and sum (rows lane/4 and lane/4 + 8)
+    float tile_max[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int key = key0 + nt * 8 + (lane & 3) * 2 + (e & 1);
+        const bool seen = key < kv_len && key >= first_key;
+        s[nt][e] = seen ? s[nt][e] * scale_log2e : -INFINITY;
+        tile_max[e >> 1] = fmaxf(tile_max[e >> 1], s[nt][e]);
+      }
+    float corr[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 1));
+      tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 2));
+      const float m_new = fmaxf(m[r], tile_max[r]);
+      corr[r] = (m_new == -INFINITY) ? 1.f : exp2f(m[r] - m_new);
+      m[r] = m_new;
+      l[r] *= corr[r];
+    }
+    uint32_t pf[4];
+    {
+      float p[2][4];
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int r = e >> 1;
+          p[nt][e] = (m[r] == -INFINITY) ? 0.f : exp2f(s[nt][e] - m[r]);
+          l[r] += p[nt][e];
+        }
+      pf[0] = mma::pack_bf16(p[0][0], p[0][1]);
+      pf[1] = mma::pack_bf16(p[0][2], p[0][3]);
+      pf[2] = mma::pack_bf16(p[1][0], p[1][1]);
+      pf[3] = mma::pack_bf16(p[1][2], p[1][3]);
+    }
+    // O = O * corr + P V
+    {
+      const int row = warp * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);   // key row
+      const int half = lane >> 4;                                           // dims 0-7 / 8-15
+#pragma unroll
+      for (int j = 0; j < D / 16; ++j) {
+        o[2 * j][0] *= corr[0]; o[2 * j][1] *= corr[0]; o[2 * j][2] *= corr[1]; o[2 * j][3] *= corr[1];
+        o[2 * j + 1][0] *= corr[0]; o[2 * j + 1][1] *= corr[0];
+        o[2 * j + 1][2] *= corr[1]; o[2 * j + 1][3] *= corr[1];
+        const int chunk = j * 2 + half;
+        uint32_t b0, b1, b2, b3;
+        mma::ldmatrix_x4_trans(mma::swizzled(vbase + (chunk >> 3) * (KT * 128), row, chunk & 7),
+                               b0, b1, b2, b3);
+        mma::bf16_16816(o[2 * j], pf, b0, b1);
+        mma::bf16_16816(o[2 * j + 1], pf, b2, b3);
+      }
+    }
+    __syncwarp();
+    if (lane == 0) tma::mbar_arrive(&empty[stage]);
+  }
+
+  // ---- merge the four warps through shared memory ------------------------------------
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
+    l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+  }
+  asm volatile("bar.sync 1, %0;" ::"n"(kComputeWarps * 32));   // every tile has been consumed
+  float* sm_o = reinterpret_cast<float*>(smem);                // [warp][16][D]
+  float* sm_m = sm_o + kComputeWarps * 16 * D;                 // [warp][16]
+  float* sm_l = sm_m + kComputeWarps * 16;
+  {
+    const int r0 = lane >> 2, c = (lane & 3) * 2;
+#pragma unroll
+    for (int nt = 0; nt < D / 8; ++nt) {
+      float* row0 = sm_o + (warp * 16 + r0) * D + nt * 8 + c;
+      float* row1 = row0 + 8 * D;
+      row0[0] = o[nt][0]; row0[1] = o[nt][1];
+      row1[0] = o[nt][2]; row1[1] = o[nt][3];
+    }
+    if ((lane & 3) == 0) {
+      sm_m[warp * 16 + r0] = m[0]; sm_m[warp * 16 + r0 + 8] = m[1];
+      sm_l[warp * 16 + r0] = l[0]; sm_l[warp * 16 + r0 + 8] = l[1];
+    }
+  }
+  asm volatile("bar.sync 1, %0;" ::"n"(kComputeWarps * 32));
+  if (!alive) return;
+  for (int r = 0; r < group; ++r) {
+    float big = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kComputeWarps; ++w) big = fmaxf(big, sm_m[w * 16 + r]);
+    float weight[kComputeWarps], total = 0.f;
+#pragma unroll
+    for (int w = 0; w < kComputeWarps; ++w) {
+      weight[w] = (sm_m[w * 16 + r] == -INFINITY) ? 0.f : exp2f(sm_m[w * 16 + r] - big);
+      total += weight[w] * sm_l[w * 16 + r];
+    }
+    const int h = g * group + r;
+    for (int dim = threadIdx.x; dim < D; dim += kComputeWarps * 32) {
+      float acc = 0.f;
+#pragma unroll
+      for (int w = 0; w < kComputeWarps; ++w) acc += weight[w] * sm_o[(w * 16 + r) * D + dim];
+      if (splits == 1) {
+        out[((long long)b * heads + h) * D + dim] = __float2bfloat16_rn(acc / total);
+      } else {
+        part_o[(((long long)b * heads + h) * splits + split) * D + dim] = acc;
+      }
+    }
+    if (splits > 1 && threadIdx.x == 0) {
+      float* ml = part_ml + (((long long)b * heads + h) * splits + split) * 2;
+      ml[0] = big;
+      ml[1] = total;
+    }
+  }
+}
+
+// out[b, h, :] = sum_s w_s o_s / sum_s w_s l_s with w_s = exp2(m_s - max m)
+__global__ void combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                               __nv_bfloat16* __restrict__ out, int splits, int head_dim) {
+  const long long bh = blockIdx.x;
+  const float* ml = part_ml + bh * splits * 2;
+  float big = -INFINITY;
+  for (int s = 0; s < splits; ++s) big = fmaxf(big, ml[2 * s]);
+  float total = 0.f;
+  for (int s = 0; s < splits; ++s)
+    total += (ml[2 * s] == -INFINITY) ? 0.f : exp2f(ml[2 * s] - big) * ml[2 * s + 1];
+  for (int dim = threadIdx.x; dim < head_dim; dim += blockDim.x) {
+    float acc = 0.f;
+    for (int s = 0; s < splits; ++s) {
+      const float w = (ml[2 * s] == -INFINITY) ? 0.f : exp2f(ml[2 * s] - big);
+      acc += w * part_o[(bh * splits + s) * head_dim + dim];
+    }
+    out[bh * head_dim + dim] = __float2bfloat16_rn(acc / total);
+  }
+}
+
+__device__ int g_error;
+
+template <int D>
+int launch(const CUtensorMap* k_map, const CUtensorMap* v_map, const __nv_bfloat16* q,
+           long long q_stride, const int32_t* seq_lens, const int32_t* block_table, int max_blocks,
+           __nv_bfloat16* out, float* part_o, float* part_ml, int sequences, int heads,
+           int kv_heads, int splits, float scale, int window, cudaStream_t stream) {
+  static bool configured = false;
+  int* error = nullptr;
+  if (cudaGetSymbolAddress(reinterpret_cast<void**>(&error), g_error) != cudaSuccess)
+    return cudaErrorInvalidValue;
+  if (!configured) {
+    const cudaError_t e = cudaFuncSetAttribute(decode_attention_kernel<D>,
+                                               cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               Smem<D>::kBytes);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    configured = true;
+  }
+  const dim3 grid(splits, kv_heads, sequences);
+  decode_attention_kernel<D><<<grid, kThreads, Smem<D>::kBytes, stream>>>(
+      *k_map, *v_map, q, q_stride, seq_lens, block_table, max_blocks, out, part_o, part_ml, heads,
+      kv_heads, splits, scale * 1.4426950408889634f, window, error);
+  int status = launch_status();
+  if (status == 0 && splits > 1) {
+    combine_kernel<<<sequences * heads, D <= 128 ? D : 128, 0, stream>>>(part_o, part_ml, out,
+                                                                         splits, D);
+    status = launch_status();
+  }
+  return status;
+}
+
+}  // namespace
+
+// A tensor map over one cache entry [blocks, kv_heads, 64, head_dim] seen as rows of
+// head_dim, read in boxes of 64 rows x 64 columns. `map` points to 128 bytes on the host.
+SAKV_EXPORT int sakv_decode_attention_map(void* map, const void* cache, long long blocks,
+                                          int kv_heads, int head_dim) {
+  if (blocks <= 0 || kv_heads <= 0 || head_dim % 64) return cudaErrorInvalidValue;
+  return tma::make_map_bf16_2d(reinterpret_cast<CUtensorMap*>(map), cache,
+                               (uint64_t)blocks * kv_heads * KT, head_dim,
+                               (uint64_t)head_dim * 2, KT, 64);
+}
+
+SAKV_EXPORT int sakv_decode_attention(const void* k_map, const void* v_map, const void* q,
+                                      long long q_stride, const int32_t* seq_lens,
+                                      const int32_t* block_table, int max_blocks, void* out,
+                                      float* part_o, float* part_ml, int sequences, int heads,
+                                      int kv_heads, int head_dim, int splits, float scale,
+                                      int window, cudaStream_t stream) {
+  if (sequences < 0 || heads <= 0 || kv_heads <= 0 || heads % kv_heads || heads / kv_heads > 16 ||
+      splits < 1 || max_blocks <= 0 || (splits > 1 && (!part_o || !part_ml)))
+    return cudaErrorInvalidValue;
+  if (sequences == 0) return 0;
+  if (sequences > 65535 || kv_heads > 65535) return cudaErrorInvalidValue;
+#define GO(D)                                                                                  \
+  return launch<D>((const CUtensorMap*)k_map, (const CUtensorMap*)v_map,                      \
+                   (const __nv_bfloat16*)q, q_stride, seq_lens, block_table, max_blocks,      \
+                   (__nv_bfloat16*)out, part_o, part_ml, sequences, heads, kv_heads, splits,  \
+                   scale, window, stream)
+  if (head_dim == 64) GO(64);
+  if (head_dim == 128) GO(128);
+#undef GO
+  return cudaErrorInvalidValue;
+}
+
+// The error word that a timed-out wait leaves (0 = none); reading it synchronises.
+SAKV_EXPORT int sakv_decode_attention_error(int* value) {
+  return static_cast<int>(cudaMemcpyFromSymbol(value, g_error, sizeof(int)));
+}

@@ -39,6 +39,8 @@ LIBRARIES = {
     "attention_plain": "attention_plain.cu",
     "gemm_f32": "gemm_f32.cu",
     "sampling": "sampling.cu",
+    "attention_decode": "attention_decode.cu",
+    "attention_prefill": "attention_prefill.cu",
 }
 
 #: extra flags of single libraries (libraries that need the driver API, for instance)

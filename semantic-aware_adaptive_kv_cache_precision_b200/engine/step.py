@@ -18,6 +18,8 @@ from dataclasses import dataclass, field
 import numpy as np
 import torch
 
+QUERY_TILE = 64       # tokens per query tile of the prefill attention kernel; also the cache block
+
 
 @dataclass
 class StepContext:
@@ -39,7 +41,7 @@ class StepContext:
     max_new: int = 0
     max_len: int = 0
     is_decode: bool = False           # every sequence brings exactly one token
-    slots_long: torch.Tensor | None = None
+    q_tiles: torch.Tensor | None = None   # int32 [n, 4]: (sequence, first row, rows, first position)
 
 
 class StepStager:
@@ -69,8 +71,18 @@ class StepStager:
         T = int(sum(counts))
         want_rows = np.asarray(want_rows, dtype=np.int32).reshape(-1)
         W = want_rows.size
+        # block lists only as wide as the longest sequence of the step needs
+        ends = [s + c for s, c in zip(starts, counts)]
+        width = max(1, -(-max(ends, default=1) // QUERY_TILE))
+        tables = [np.ascontiguousarray(t[:, :min(width, t.shape[1])]) for t in tables]
+        # query tiles of up to 64 tokens, none crossing a sequence's end
+        tiles, row = [], 0
+        for i, (s, c) in enumerate(zip(starts, counts)):
+            for a in range(0, c, QUERY_TILE):
+                tiles.append((i, row + a, min(QUERY_TILE, c - a), s + a))
+            row += c
         fields = [("token_ids", T), ("positions", T), ("token_seq", T), ("cu_seqlens", B + 1),
-                  ("seq_lens", B), ("slots", B), ("want", W)]
+                  ("seq_lens", B), ("slots", B), ("want", W), ("q_tiles", 4 * len(tiles))]
         fields += [(f"table{g}", t.size) for g, t in enumerate(tables)]
         offsets, total = {}, 0
         for name, n in fields:
@@ -96,6 +108,7 @@ class StepStager:
         put("seq_lens", [s + c for s, c in zip(starts, counts)])
         put("slots", slots)
         put("want", want_rows)
+        put("q_tiles", np.asarray(tiles, dtype=np.int32))
         for g, t in enumerate(tables):
             put(f"table{g}", t)
         self.last_bytes = 4 * total
@@ -107,11 +120,11 @@ class StepStager:
             return self.dev[offsets[name]:offsets[name] + n]
 
         dev_tables = [view(f"table{g}", t.size).view(t.shape) for g, t in enumerate(tables)]
-        ends = [s + c for s, c in zip(starts, counts)]
         return StepContext(
             tokens=T, sequences=B, token_ids=view("token_ids", T), positions=view("positions", T),
             token_seq=view("token_seq", T), cu_seqlens=view("cu_seqlens", B + 1),
             seq_lens=view("seq_lens", B), slots=view("slots", B), want=view("want", W),
             tables=dev_tables, new_counts=counts, starts=list(starts), host_slots=list(slots),
             max_position=max(ends) - 1 if ends else 0, max_new=max(counts, default=0),
-            max_len=max(ends, default=0), is_decode=all(c == 1 for c in counts))
+            max_len=max(ends, default=0), is_decode=all(c == 1 for c in counts),
+            q_tiles=view("q_tiles", 4 * len(tiles)).view(len(tiles), 4))

@@ -12,9 +12,12 @@ import torch
 
 from ._lib import BF16, CACHE_BLOCK, F32, KernelError, call, dtype_code, ptr, require_cuda
 from .linear import linear
+from .attention import (attention_decode, attention_prefill, decode_splits, fast_path_takes,
+                        kernel_errors)
 
 __all__ = ["CACHE_BLOCK", "KernelError", "embed", "rms_norm", "rope_store", "attention_plain",
-           "gated_silu", "add_into", "linear", "choose"]
+           "attention_decode", "attention_prefill", "decode_splits", "fast_path_takes",
+           "kernel_errors", "gated_silu", "add_into", "linear", "choose"]
 
 
 def _check(cond: bool, message: str) -> None:

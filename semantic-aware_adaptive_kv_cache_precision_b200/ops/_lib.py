@@ -30,6 +30,17 @@ SIGNATURES = {
                              [P, I, L, P, P, P, P, P, P, I, I, I, I, I, F, I, P]),
     "sakv_gemm_f32": ("gemm_f32", [P, L, P, P, P, L, I, I, I, I, P]),
     "sakv_choose": ("sampling", [P, L, I, I, F, U, P, P, P, P]),
+    "sakv_decode_attention": ("attention_decode",
+                              [P, P, P, L, P, P, I, P, P, P, I, I, I, I, I, F, I, P]),
+    "sakv_prefill_attention": ("attention_prefill",
+                               [P, P, P, L, P, P, I, P, P, I, I, I, I, F, I, P]),
+}
+
+#: functions without a stream argument: (library, argument types)
+PLAIN_SIGNATURES = {
+    "sakv_decode_attention_map": ("attention_decode", [P, P, L, I, I]),
+    "sakv_decode_attention_error": ("attention_decode", [P]),
+    "sakv_prefill_attention_error": ("attention_prefill", [P]),
 }
 
 _functions: dict[str, object] = {}
@@ -39,6 +50,17 @@ def function(name: str):
     fn = _functions.get(name)
     if fn is None:
         library, argtypes = SIGNATURES[name]
+        fn = getattr(_build.load(library), name)
+        fn.argtypes = argtypes
+        fn.restype = c_int
+        _functions[name] = fn
+    return fn
+
+
+def plain_function(name: str):
+    fn = _functions.get(name)
+    if fn is None:
+        library, argtypes = PLAIN_SIGNATURES[name]
         fn = getattr(_build.load(library), name)
         fn.argtypes = argtypes
         fn.restype = c_int

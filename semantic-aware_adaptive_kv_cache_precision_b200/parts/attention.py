@@ -83,7 +83,19 @@ class GQAAttention(Part):
         ops.linear(attended, self.w_o, self.b_o, accumulate_into=residual)
 
     def attend(self, qkv, step, view):
+        """Tensor-core kernels where they take the sizes (bf16, head_dim 64 or 128, up
+        to 16 query heads per KV head): the split-key decode kernel when every
+        sequence brings one token, the causal prefill kernel otherwise. Everything
+        else, and the whole fp32 path, runs the plain kernel."""
         s = self.spec
+        if ops.fast_path_takes(qkv.dtype, s.heads, s.kv_heads, s.head_dim):
+            if step.is_decode:
+                return ops.attention_decode(qkv, view.keys, view.values, step.seq_lens,
+                                            view.block_table, s.heads, s.kv_heads, s.head_dim,
+                                            s.scale, s.window, step.max_len)
+            return ops.attention_prefill(qkv, view.keys, view.values, step.q_tiles,
+                                         step.seq_lens, view.block_table, s.heads, s.kv_heads,
+                                         s.head_dim, s.scale, s.window)
         return ops.attention_plain(qkv, view.keys, view.values, step.positions, step.token_seq,
                                    view.block_table, s.heads, s.kv_heads, s.head_dim, s.scale,
                                    s.window)

@@ -56,7 +56,26 @@ TINY_W = {
     "use_sliding_window": True, "sliding_window": 70, "max_window_layers": 1,
     "eos_token_id": 5,
 }
-TINY = {"A": (TINY_A, 0), "B": (TINY_B, 1), "W": (TINY_W, 2)}
+# head sizes that the bf16 tensor-core attention kernels take: 64 with a window, and
+# Qwen2.5's own 128 with 6 query heads per KV head
+TINY_C = {
+    "architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2",
+    "num_hidden_layers": 3, "hidden_size": 128, "num_attention_heads": 2,
+    "num_key_value_heads": 1, "intermediate_size": 208, "vocab_size": 257,
+    "max_position_embeddings": 1024, "rope_theta": 20000.0, "rms_norm_eps": 2e-6,
+    "tie_word_embeddings": False, "hidden_act": "silu", "torch_dtype": "float32",
+    "use_sliding_window": True, "sliding_window": 130, "max_window_layers": 2,
+    "eos_token_id": 3,
+}
+TINY_D = {
+    "architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2",
+    "num_hidden_layers": 2, "hidden_size": 384, "num_attention_heads": 12,
+    "num_key_value_heads": 2, "head_dim": 128, "intermediate_size": 320, "vocab_size": 400,
+    "max_position_embeddings": 2048, "rope_theta": 1000000.0, "rms_norm_eps": 1e-6,
+    "tie_word_embeddings": True, "hidden_act": "silu", "torch_dtype": "float32",
+    "use_sliding_window": False, "eos_token_id": 9,
+}
+TINY = {"A": (TINY_A, 0), "B": (TINY_B, 1), "W": (TINY_W, 2), "C": (TINY_C, 3), "D": (TINY_D, 4)}
 
 
 @pytest.fixture(scope="session")

@@ -13,7 +13,7 @@ from helpers import assert_close_to_plain, assert_same_logits, plain_logits
 pytestmark = pytest.mark.gpu
 
 DTYPES = ["float32", "bfloat16"]
-NAMES = ["A", "B", "W"]
+NAMES = ["A", "B", "W", "C", "D"]
 
 
 def engine_for(folder, dtype, **kw):
@@ -43,7 +43,8 @@ def engines(model_folders):
 def test_each_request_alone_and_whole(name, dtype, engines, model_folders):
     engine = engines(name, dtype)
     folder = model_folders(name, stored(dtype))
-    lengths = {"A": [5, 11, 17, 100], "B": [1, 7, 30, 64, 200], "W": [3, 69, 70, 71, 150, 300]}[name]
+    lengths = {"A": [5, 11, 17, 100], "B": [1, 7, 30, 64, 200], "W": [3, 69, 70, 71, 150, 300],
+               "C": [1, 64, 129, 131, 400], "D": [2, 65, 300]}[name]
     for ids in prompts_for(name, lengths):
         got = engine.forward(ids)
         assert_close_to_plain(got, plain_logits(folder, ids), dtype, f"{name} len {len(ids)}")
@@ -56,7 +57,8 @@ def test_each_request_alone_and_whole(name, dtype, engines, model_folders):
 def test_last_32_tokens_one_by_one(name, dtype, engines, model_folders):
     engine = engines(name, dtype)
     folder = model_folders(name, stored(dtype))
-    for ids in prompts_for(name, {"A": [40, 120], "B": [33, 130], "W": [100, 260]}[name], seed=1):
+    for ids in prompts_for(name, {"A": [40, 120], "B": [33, 130], "W": [100, 260],
+                                 "C": [33, 300], "D": [150]}[name], seed=1):
         whole = engine.forward(ids)
         (slot,) = engine.open(1)
         head = len(ids) - 32
@@ -79,7 +81,9 @@ def test_unequal_batches_one_after_another(name, dtype, model_folders):
     engine = engine_for(folder, dtype, max_tokens=8 * 64)
     batches = {"A": [[5, 11, 17], [64, 3, 30], [1, 90, 65]],
                "B": [[1, 7, 30, 64], [2, 100, 33, 5], [64, 65, 1, 128]],
-               "W": [[3, 75, 140], [71, 70, 69], [1, 200, 64]]}[name]
+               "W": [[3, 75, 140], [71, 70, 69], [1, 200, 64]],
+               "C": [[1, 140, 64], [100, 120, 60], [2, 250, 63]],
+               "D": [[5, 130, 64], [1, 200, 33], [100, 3, 66]]}[name]
     extra = [6, 2, 9, 4]                    # decode steps per request; unequal, so some end early
     for b, lengths in enumerate(batches):
         prompts = prompts_for(name, [n + e for n, e in zip(lengths, extra)], seed=10 + b)

@@ -337,3 +337,137 @@ def test_kernels_refuse_what_they_cannot_take():
                             torch.zeros(1, dtype=torch.int32, device=DEV),
                             torch.zeros(1, dtype=torch.int32, device=DEV),
                             torch.zeros((1, 1), dtype=torch.int32, device=DEV), 1, 1, 512, 1.0, None)
+
+
+# ---- the bfloat16 tensor-core attention kernels ------------------------------------------
+
+def paged_case(rng, lengths, kv_heads, d, n_blocks=64, poison=True):
+    """A cache with scattered blocks for sequences of the given lengths. Blocks that no
+    sequence holds, and the places past each sequence's end, are NaN."""
+    k = rng.standard_normal((n_blocks, kv_heads, 64, d))
+    v = rng.standard_normal((n_blocks, kv_heads, 64, d))
+    order = rng.permutation(n_blocks)
+    width = max(-(-n // 64) for n in lengths)
+    table = np.full((len(lengths), width), -1, dtype=np.int32)
+    used = np.zeros((n_blocks, 64), dtype=bool)
+    at = 0
+    for i, n in enumerate(lengths):
+        for b in range(-(-n // 64)):
+            table[i, b] = order[at]
+            used[order[at], :min(64, n - 64 * b)] = True
+            at += 1
+    assert at <= n_blocks
+    if poison:                       # `used` is [block, place]: spread it over the heads
+        k.transpose(0, 2, 1, 3)[~used] = np.nan
+        v.transpose(0, 2, 1, 3)[~used] = np.nan
+    return dev(k, torch.bfloat16), dev(v, torch.bfloat16), table
+
+
+def sequence_kv(cache, table_row, length):
+    c = host(cache)
+    out = np.zeros((length,) + c.shape[1:2] + c.shape[3:])
+    for p in range(length):
+        out[p] = c[table_row[p // 64], :, p % 64]
+    return out
+
+
+@pytest.mark.parametrize("heads,kv_heads,d,window", [(12, 2, 128, None), (4, 4, 64, None),
+                                                     (16, 1, 128, None), (6, 3, 64, 100),
+                                                     (14, 2, 128, 64), (5, 5, 128, 1)])
+@pytest.mark.parametrize("splits", [1, 3, None])
+def test_attention_decode_kernel(heads, kv_heads, d, window, splits):
+    rng = np.random.default_rng(heads * d + (window or 0))
+    lengths = [1, 63, 64, 65, 700, 2048, 129]
+    k_cache, v_cache, table = paged_case(rng, lengths, kv_heads, d)
+    if window:          # blocks wholly before the window may be gone
+        for i, n in enumerate(lengths):
+            table[i, :max(0, n - window) // 64] = -1
+    B = len(lengths)
+    width = (heads + 2 * kv_heads) * d
+    qkv = dev(rng.standard_normal((B, width)), torch.bfloat16)
+    scale = d ** -0.5
+    got = ops.attention_decode(qkv, k_cache, v_cache, dev(lengths, torch.int32),
+                               dev(table, torch.int32), heads, kv_heads, d, scale, window,
+                               max(lengths), splits=splits)
+    assert ops.kernel_errors() == {"sakv_decode_attention_error": 0,
+                                   "sakv_prefill_attention_error": 0}
+    q = host(qkv)[:, :heads * d].reshape(B, heads, d)
+    for i, n in enumerate(lengths):
+        first = max(0, n - window) if window else 0
+        kk, vv = np.zeros((n, kv_heads, d)), np.zeros((n, kv_heads, d))
+        kc, vc = host(k_cache), host(v_cache)
+        for p in range(first, n):
+            kk[p], vv[p] = kc[table[i, p // 64], :, p % 64], vc[table[i, p // 64], :, p % 64]
+        want = attention_reference(q[i], kk, vv, n - 1, heads, kv_heads, scale, window)
+        np.testing.assert_allclose(host(got[i]).reshape(heads, d), want, rtol=0, atol=1.5e-2,
+                                   err_msg=f"sequence {i} of length {n}")
+    # the plain kernel agrees too (same inputs, same cache)
+    pos = dev([n - 1 for n in lengths], torch.int32)
+    plain_out = ops.attention_plain(qkv, k_cache, v_cache, pos, dev(np.arange(B), torch.int32),
+                                    dev(table, torch.int32), heads, kv_heads, d, scale, window)
+    np.testing.assert_allclose(host(got), host(plain_out), rtol=0, atol=2e-2)
+
+
+@pytest.mark.parametrize("heads,kv_heads,d,window", [(12, 2, 128, None), (2, 1, 64, None),
+                                                     (6, 6, 64, 70), (7, 1, 128, 200)])
+def test_attention_prefill_kernel(heads, kv_heads, d, window):
+    rng = np.random.default_rng(heads + d + (window or 0))
+    # (cached before the step, new tokens): whole prompts, one that ends on a block's
+    # edge, a chunk that continues a long prefix, single tokens
+    cases = [(0, 150), (0, 64), (299, 1), (64, 2), (100, 130), (0, 1), (37, 91), (600, 200)]
+    lengths = [a + n for a, n in cases]
+    k_cache, v_cache, table = paged_case(rng, lengths, kv_heads, d)
+    T = sum(n for _, n in cases)
+    width = (heads + 2 * kv_heads) * d
+    qkv = dev(rng.standard_normal((T, width)), torch.bfloat16)
+    tiles, row = [], 0
+    for i, (a, n) in enumerate(cases):
+        for s in range(0, n, 64):
+            tiles.append((i, row + s, min(64, n - s), a + s))
+        row += n
+    scale = d ** -0.5
+    got = ops.attention_prefill(qkv, k_cache, v_cache, dev(tiles, torch.int32),
+                                dev(lengths, torch.int32), dev(table, torch.int32), heads,
+                                kv_heads, d, scale, window)
+    assert ops.kernel_errors()["sakv_prefill_attention_error"] == 0
+    q = host(qkv)[:, :heads * d].reshape(T, heads, d)
+    row = 0
+    for i, (a, n) in enumerate(cases):
+        kk = sequence_kv(k_cache, table[i], lengths[i])
+        vv = sequence_kv(v_cache, table[i], lengths[i])
+        for t in range(n):
+            want = attention_reference(q[row + t], kk, vv, a + t, heads, kv_heads, scale, window)
+            np.testing.assert_allclose(host(got[row + t]).reshape(heads, d), want, rtol=0,
+                                       atol=1.5e-2, err_msg=f"case {i}, token {t}")
+        row += n
+
+
+@pytest.mark.parametrize("kernel", ["decode", "prefill"])
+def test_tensor_core_attention_finds_one_far_key(kernel):
+    rng = np.random.default_rng(11)
+    heads, kv_heads, d = 12, 2, 128
+    n = 1500
+    k_cache, v_cache, table = paged_case(rng, [n], kv_heads, d, n_blocks=32)
+    k_cache *= 0.05
+    direction = rng.standard_normal(d)
+    direction /= np.linalg.norm(direction)
+    for far in (0, 63, 64, 777, 1471, 1472, 1499):
+        kc = k_cache.clone()
+        kc[table[0, far // 64], 1, far % 64] = dev(direction * 60.0, torch.bfloat16)
+        q = np.zeros((1, heads + 2 * kv_heads, d))
+        q[0, 6:12] = direction * 60.0                     # the heads of KV head 1
+        qkv = dev(q.reshape(1, -1), torch.bfloat16)
+        if kernel == "decode":
+            got = ops.attention_decode(qkv, kc, v_cache, dev([n], torch.int32),
+                                       dev(table, torch.int32), heads, kv_heads, d, d ** -0.5,
+                                       None, n)
+        else:
+            got = ops.attention_prefill(qkv, kc, v_cache, dev([(0, 0, 1, n - 1)], torch.int32),
+                                        dev([n], torch.int32), dev(table, torch.int32), heads,
+                                        kv_heads, d, d ** -0.5, None)
+        want = host(v_cache)[table[0, far // 64], 1, far % 64]
+        out = host(got).reshape(heads, d)
+        for h in range(6, 12):
+            np.testing.assert_allclose(out[h], want, rtol=0, atol=2e-2,
+                                       err_msg=f"{kernel}: far key at {far}, head {h}")
+        assert np.abs(out[0] - want).max() > 0.1
