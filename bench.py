@@ -131,6 +131,118 @@ def prefill_flops(cfg, tokens: int) -> float:
     return L * (linear + attention) + 2.0 * H * V
 
 
+def reference_arm(args) -> int:
+    """The unmodified reference, installed under baseline/_ref, through its own public
+    API: `Engine(model_dir).load_weights()` and `generate(ids, n, stop_at_eos=False)`
+    (`src/microinfer/engine.py:822-833, 927-974, 1180-1206`). It runs one sequence at a
+    time and has no batch dimension, so the batch's sequences are generated one after
+    the other and the decoded tokens of all of them are divided by the time they took;
+    decode time is time(K+1 tokens) - time(1 token), as the reference's own
+    `tools/throughput.py:66-73, 278-288` measures it. Its weights are the same
+    Qwen2.5-1.5B-shaped random checkpoint, written to a temporary folder."""
+    def unavailable(why: str) -> int:
+        print(json.dumps({"impl": "reference", "unavailable": why}))
+        return 0
+
+    ref = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref, "microinfer")):
+        return unavailable("baseline/_ref is absent: the reference was not installed on this box")
+    import shutil
+    import tempfile
+    try:
+        import numpy as np
+        import torch
+        import semantic_aware_adaptive_kv_cache_precision_b200 as sakv
+        from semantic_aware_adaptive_kv_cache_precision_b200.engine.model import DecoderModel
+        from semantic_aware_adaptive_kv_cache_precision_b200.weights import write_safetensors
+        if not torch.cuda.is_available():
+            return unavailable("no CUDA device")
+        raw = dict(QWEN25_1P5B)
+        full_layers = raw["num_hidden_layers"]
+        if args.layers:
+            raw["num_hidden_layers"] = args.layers
+        cfg = sakv.config_from_dict(raw)
+        tmp = tempfile.mkdtemp(prefix="sakv_ref_")
+        try:
+            # the folder's name is how the reference recognises the model (its VERIFIED table)
+            folder = os.path.join(tmp, "qwen2.5-1.5b-instruct")
+            os.makedirs(folder)
+            card = dict(raw, attention_dropout=0.0, bos_token_id=151643, initializer_range=0.02,
+                        max_window_layers=21, sliding_window=32768, use_cache=True,
+                        transformers_version="4.43.1")
+            json.dump(card, open(os.path.join(folder, "config.json"), "w"))
+            gen = torch.Generator(device="cuda")
+            gen.manual_seed(0)
+
+            class Maker:
+                def __init__(self, d):
+                    self.shape, self.dtype, self.d = tuple(d.shape), torch.bfloat16, d
+
+                def __call__(self):
+                    t = torch.randn(self.shape, generator=gen, device="cuda") * 0.02
+                    if self.d.init == "ones_normal":
+                        t += 1.0
+                    return t.to(torch.bfloat16).cpu()
+
+            decls = DecoderModel.tensor_decls_of(cfg.model_spec())
+            write_safetensors(os.path.join(folder, "model.safetensors"),
+                              {d.name: Maker(d) for d in decls})
+            torch.cuda.empty_cache()
+            sys.path.insert(0, ref)
+            import microinfer
+            engine = microinfer.Engine(folder, verify=not args.layers)
+            engine.load_weights()
+            rng = np.random.default_rng(0)
+            K, W = args.steps, args.warmup
+            prompts = [rng.integers(0, cfg.vocab_size, CONTEXT).astype(np.int32)
+                       for _ in range(args.batch)]
+
+            def timed(ids, n):
+                began = time.perf_counter()
+                out = engine.generate(ids, n, stop_at_eos=False)
+                assert len(out) == n
+                return time.perf_counter() - began
+
+            for _ in range(max(1, W // 3)):
+                timed(prompts[0], 4)
+            sampler = ClockSampler()
+            sampler.start()
+            decode_s, prefill_s = 0.0, []
+            for ids in prompts:
+                first = timed(ids, 1)
+                decode_s += max(timed(ids, K + 1) - first, 1e-9)
+                prefill_s.append(first)
+            clocks = sampler.stop()
+        finally:
+            shutil.rmtree(tmp, ignore_errors=True)
+    except Exception as exc:          # the reference could not run here: say why, exit 0
+        return unavailable(f"{type(exc).__name__}: {str(exc)[:300]}")
+    value = args.batch * K / decode_s
+    prefill_ms = statistics.median(prefill_s) * 1e3
+    pk = peaks()
+    print(json.dumps({
+        "metric": "decode tokens/s (Qwen2.5-1.5B shape, batch 8, 2048 cached tokens)",
+        "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W,
+        "ms_per_step": round(decode_s / K * 1e3, 4), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "fp16", "impl": "reference",
+        "data": "synthetic: random weights, random token ids",
+        "config": {"model": "Qwen2.5-1.5B shape", "layers": cfg.num_hidden_layers,
+                   "layers_of_model": full_layers, "global_batch": args.batch,
+                   "seq_len": CONTEXT, "new_tokens": K,
+                   "parallelism": "single GPU; the reference has no batch dimension, the "
+                                  "batch's sequences run one after the other",
+                   "timing": "wall clock around Engine.generate, as tools/throughput.py"},
+        "prefill": {"value": round(PREFILL_TOKENS / (prefill_ms / 1e3), 1),
+                    "tokens": PREFILL_TOKENS, "ms": round(prefill_ms, 3),
+                    "frac": round(prefill_flops(cfg, PREFILL_TOKENS) / (prefill_ms / 1e3) / 1e12
+                                  / pk.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"]), 4)},
+        "points": {"decode_b1": round(value, 1)},
+        "clocks": clocks,
+        "e2e": {"value": round(value, 1), "unit": "tokens/s",
+                "h2d_bytes_per_step": 8, "d2h_bytes_per_step": 4}}))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -144,19 +256,13 @@ def main() -> int:
     ap.add_argument("--no-e2e", action="store_true")
     args = ap.parse_args()
 
-    if args.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable":
-                          "the reference builds a pybind11/CUDA extension for the local GPU with "
-                          "scikit-build-core and needs the `tokenizers` wheel and real checkpoints; "
-                          "it has no random-weights mode and no batch dimension, so it cannot run "
-                          "this metric offline"}))
-        return 0
     if args.gpus != 1:
         print(f"bench.py: this library runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
     if args.warmup < 3:
         args.warmup = 3
-
+    if args.impl == "reference":
+        return reference_arm(args)
     import numpy as np
     import torch
     import semantic_aware_adaptive_kv_cache_precision_b200 as sakv

@@ -22,6 +22,7 @@ import shutil
 import subprocess
 import sys
 import tempfile
+import threading
 import time
 from pathlib import Path
 
@@ -60,18 +61,26 @@ def _nvcc() -> str:
     return found
 
 
+_dir_lock = threading.Lock()
+_dir: Path | None = None
+
+
 def _build_dir() -> Path:
-    preferred = HERE / "_build"
-    try:
-        preferred.mkdir(exist_ok=True)
-        probe = preferred / f".write_probe_{os.getpid()}"
-        probe.write_text("")
-        probe.unlink()
-        return preferred
-    except OSError:
-        fallback = Path(tempfile.gettempdir()) / f"sakv_b200_build_{os.getuid()}"
-        fallback.mkdir(parents=True, exist_ok=True)
-        return fallback
+    """Decided once per process (several threads may ask at the same time)."""
+    global _dir
+    with _dir_lock:
+        if _dir is None:
+            preferred = HERE / "_build"
+            try:
+                preferred.mkdir(exist_ok=True)
+                probe = preferred / f".write_probe_{os.getpid()}_{threading.get_ident()}"
+                probe.write_text("")
+                probe.unlink()
+                _dir = preferred
+            except OSError:
+                _dir = Path(tempfile.gettempdir()) / f"sakv_b200_build_{os.getuid()}"
+                _dir.mkdir(parents=True, exist_ok=True)
+        return _dir
 
 
 def _headers() -> list[Path]:

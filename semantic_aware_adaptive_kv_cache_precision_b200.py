@@ -19,3 +19,8 @@ if __spec__ is not None:
 with open(_os.path.join(_HOME, "__init__.py"), encoding="utf-8") as _f:
     exec(compile(_f.read(), _os.path.join(_HOME, "__init__.py"), "exec"))
 del _f
+
+if __name__ == "__main__":      # python -m semantic_aware_adaptive_kv_cache_precision_b200 ...
+    import sys as _sys
+    from importlib import import_module as _import
+    _sys.exit(_import("semantic_aware_adaptive_kv_cache_precision_b200.cli").main())
