@@ -4,10 +4,17 @@
 The folder carries the project's name, which has a hyphen and so cannot be
 written in an ``import`` statement. This module stands in for it: it points
 ``__path__`` at the folder, so that every sub-package is found there, and runs
-the folder's ``__init__.py`` in its own namespace.
+the folder's ``__init__.py`` in its own namespace. Run with ``python -m`` it is
+the command line (``cli.py`` of the package).
 """
 
 import os as _os
+
+if __name__ == "__main__":
+    import sys as _sys
+    from importlib import import_module as _import
+    _sys.path.insert(0, _os.path.dirname(_os.path.abspath(__file__)))
+    _sys.exit(_import("semantic_aware_adaptive_kv_cache_precision_b200.cli").main())
 
 _HOME = _os.path.join(_os.path.dirname(_os.path.abspath(__file__)),
                       "semantic-aware_adaptive_kv_cache_precision_b200")
@@ -19,8 +26,3 @@ if __spec__ is not None:
 with open(_os.path.join(_HOME, "__init__.py"), encoding="utf-8") as _f:
     exec(compile(_f.read(), _os.path.join(_HOME, "__init__.py"), "exec"))
 del _f
-
-if __name__ == "__main__":      # python -m semantic_aware_adaptive_kv_cache_precision_b200 ...
-    import sys as _sys
-    from importlib import import_module as _import
-    _sys.exit(_import("semantic_aware_adaptive_kv_cache_precision_b200.cli").main())
