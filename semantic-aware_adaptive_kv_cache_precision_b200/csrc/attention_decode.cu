@@ -351,3 +351,74 @@ SAKV_EXPORT int sakv_decode_attention(const void* k_map, const void* v_map, cons
 SAKV_EXPORT int sakv_decode_attention_error(int* value) {
   return static_cast<int>(cudaMemcpyFromSymbol(value, g_error, sizeof(int)));
 }
+
+// ---- the same kernels for callers that cannot allocate (see attention_decode_static.h) ----
+#include "attention_decode_static.h"
+#include <stdio.h>
+
+namespace {
+
+// Scratch for the split partials, inside the library. In host code this name is only
+// a stand-in for the symbol: the device address must be asked for.
+static __device__ __align__(256) float g_static_scratch[SAKV_DECODE_STATIC_SCRATCH_FLOATS];
+
+constexpr int kMaxDevices = 64;
+float* g_static_scratch_address[kMaxDevices];   // per device, looked up at its first call
+
+void say(char* why, int why_len, const char* text) {
+  if (why && why_len > 0) snprintf(why, static_cast<size_t>(why_len), "%s", text);
+}
+
+}  // namespace
+
+SAKV_EXPORT int sakv_decode_attention_static_scratch(
+    const void* k_map, const void* v_map, const void* q, long long q_stride,
+    const int32_t* seq_lens, const int32_t* block_table, int max_blocks, void* out, int sequences,
+    int heads, int kv_heads, int head_dim, int splits, float scale, int window, char* why,
+    int why_len, cudaStream_t stream) {
+  if (sequences < 0 || heads <= 0 || kv_heads <= 0 || heads % kv_heads || heads / kv_heads > 16 ||
+      splits < 1 || max_blocks <= 0 || (head_dim != 64 && head_dim != 128) || sequences > 65535) {
+    say(why, why_len, "decode attention: a size is outside what the kernel takes (head_dim 64 or "
+                      "128, at most 16 query heads per KV head, at least one split)");
+    return cudaErrorInvalidValue;
+  }
+  const long long need = (long long)sequences * heads * splits * (head_dim + 2);
+  if (need > SAKV_DECODE_STATIC_SCRATCH_FLOATS) {
+    if (why && why_len > 0)
+      snprintf(why, static_cast<size_t>(why_len),
+               "decode attention without allocation: sequences * heads * splits * (head_dim + 2) "
+               "= %lld floats, the built-in scratch holds %d; use fewer splits or sequences, or "
+               "the entry point that takes scratch buffers",
+               need, SAKV_DECODE_STATIC_SCRATCH_FLOATS);
+    return cudaErrorInvalidValue;
+  }
+  if (sequences == 0) return 0;
+  int device = 0;
+  cudaError_t e = cudaGetDevice(&device);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  if (device < 0 || device >= kMaxDevices) {
+    say(why, why_len, "decode attention without allocation: device index beyond 63");
+    return cudaErrorInvalidValue;
+  }
+  if (!g_static_scratch_address[device]) {
+    // once per device, with that device current: the array's address on THIS device
+    float* address = nullptr;
+    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&address), g_static_scratch);
+    if (e != cudaSuccess || !address) {
+      say(why, why_len, "decode attention without allocation: cudaGetSymbolAddress failed");
+      return static_cast<int>(e != cudaSuccess ? e : cudaErrorInvalidValue);
+    }
+    g_static_scratch_address[device] = address;
+  }
+  float* part_o = g_static_scratch_address[device];
+  float* part_ml = part_o + (long long)sequences * heads * splits * head_dim;
+  if (head_dim == 64)
+    return launch<64>((const CUtensorMap*)k_map, (const CUtensorMap*)v_map,
+                      (const __nv_bfloat16*)q, q_stride, seq_lens, block_table, max_blocks,
+                      (__nv_bfloat16*)out, part_o, part_ml, sequences, heads, kv_heads, splits,
+                      scale, window, stream);
+  return launch<128>((const CUtensorMap*)k_map, (const CUtensorMap*)v_map,
+                     (const __nv_bfloat16*)q, q_stride, seq_lens, block_table, max_blocks,
+                     (__nv_bfloat16*)out, part_o, part_ml, sequences, heads, kv_heads, splits,
+                     scale, window, stream);
+}
