@@ -42,6 +42,7 @@ LIBRARIES = {
     "sampling": "sampling.cu",
     "attention_decode": "attention_decode.cu",
     "attention_prefill": "attention_prefill.cu",
+    "gemm_tc": "gemm_tc.cu",
 }
 
 #: extra flags of single libraries (libraries that need the driver API, for instance)

@@ -1,0 +1,310 @@
+// The bf16 matrix product of the serving path on tcgen05 tensor cores:
+//
+//   C[m, n] = sum_k X[m, k] W[n, k]   (+ bias[n])        X: [M, K] activations, bf16
+//                                                          W: [N, K] weights as stored, bf16
+// computed "weights on the rows": a block owns 128 rows of W (the M dimension of a
+// 128 x MT x 16 tcgen05.mma) and up to MT tokens (its N dimension, 16..256), so a
+// decode step with a handful of tokens still streams every weight through full-width
+// tensor-core instructions. Both operands are K-major tiles of 64 columns that TMA
+// drops into shared memory with the 128-byte swizzle; a ring of stages guarded by
+// full/empty mbarriers keeps many tiles in flight; the fp32 accumulator lives in
+// tensor memory (one weight row per lane, one token per column), is read back with
+// tcgen05.ld and finished in registers:
+//
+//   out_bf16 / out_f32 : C (+ bias)                    QKV projection, LM head
+//   accumulate_f32     : R[m, n] += C                  o_proj and down_proj into the residual
+//   gated_silu         : silu(C_gate) * C_up           gate and up rows [n] and [n + I] of one
+//                                                      matrix, two accumulators side by side
+//
+// With few tokens and a small N there are too few row tiles to fill 148 SMs, so K is
+// split over blockIdx.z: every split writes its partial tile to scratch, takes a
+// ticket, and the last one adds the partials in split order (the same order every
+// time) and runs the epilogue. The reference calls cuBLAS for all of this
+// (`src/core_kernels/linear.cu:85-142`); warps: 0 = TMA, 1 = MMA issue and tensor
+// memory, 2..5 = epilogue. No cluster multicast anywhere.
+#include "common.cuh"
+#include "tcgen05.cuh"
+#include "tma.cuh"
+
+namespace {
+
+constexpr int BM = 128;          // weight rows per block (MMA M)
+constexpr int BK = 64;           // columns per stage (one 128-byte swizzle row)
+constexpr int kThreads = 192;
+constexpr int kWTile = BM * BK * 2;
+constexpr int kSmemBudget = 200 * 1024;
+
+enum : int { EPI_BF16 = 0, EPI_F32 = 1, EPI_ACCUM = 2, EPI_GATED = 3 };
+
+struct Params {
+  int M, N, K;
+  int splits, kb_per_split;
+  int dual_offset;       // row of W where the "up" half starts (gated_silu)
+  int epi;
+  const void* bias;      // [N] or null
+  int bias_dtype;
+  void* out;             // [M, ldo]
+  long long ldo;
+  float* partial;        // scratch of the splits
+  int* tickets;          // one counter per tile, zero before and after every launch
+  int* error;
+};
+
+template <int MT, bool kDual>
+struct Cfg {
+  static constexpr int kXTile = MT * BK * 2;
+  static constexpr int kStageBytes = (kDual ? 2 : 1) * kWTile + kXTile;
+  static constexpr int kStagesRaw = kSmemBudget / kStageBytes;
+  static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
+  static constexpr int kAcc = (kDual ? 2 : 1) * MT;
+  static constexpr int kTmemCols = kAcc <= 32 ? 32 : kAcc <= 64 ? 64 : kAcc <= 128 ? 128
+                                   : kAcc <= 256 ? 256 : 512;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
+};
+
+__device__ __forceinline__ float bias_at(const Params& p, int n) {
+  if (!p.bias || n >= p.N) return 0.f;
+  return p.bias_dtype == SAKV_F32 ? reinterpret_cast<const float*>(p.bias)[n]
+                                  : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.bias)[n]);
+}
+
+__device__ __forceinline__ void finish(const Params& p, int m, int n, float c, float up,
+                                       float bias) {
+  if (m >= p.M || n >= p.N) return;
+  const long long at = (long long)m * p.ldo + n;
+  if (p.epi == EPI_BF16) {
+    reinterpret_cast<__nv_bfloat16*>(p.out)[at] = __float2bfloat16_rn(c + bias);
+  } else if (p.epi == EPI_F32) {
+    reinterpret_cast<float*>(p.out)[at] = c + bias;
+  } else if (p.epi == EPI_ACCUM) {
+    reinterpret_cast<float*>(p.out)[at] += c + bias;
+  } else {
+    const float silu = c / (1.0f + expf(-c));
+    reinterpret_cast<__nv_bfloat16*>(p.out)[at] = __float2bfloat16_rn(silu * up);
+  }
+}
+
+template <int MT, bool kDual>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant__ CUtensorMap x_map,
+               const Params p) {
+  using C = Cfg<MT, kDual>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~uintptr_t(1023));
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + C::kStages * C::kStageBytes);
+  uint64_t* empty = full + C::kStages;
+  uint64_t* accum = empty + C::kStages;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum + 1);
+  int* last_flag = reinterpret_cast<int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_tile = blockIdx.x, m_tile = blockIdx.y, split = blockIdx.z;
+  const int n0 = n_tile * BM, m0 = m_tile * MT;
+  const int total_kb = (p.K + BK - 1) / BK;
+  const int kb0 = split * p.kb_per_split;
+  const int kb1 = min(total_kb, kb0 + p.kb_per_split);
+  const int n_kb = kb1 - kb0;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::kStages; ++s) {
+      tma::mbar_init(&full[s], 1);
+      tma::mbar_init(&empty[s], 1);
+    }
+    tma::mbar_init(accum, 1);
+    tma::fence_barrier_init();
+  }
+  if (warp == 1) tc::tmem_alloc(tmem_slot, C::kTmemCols);
+  tc::fence_before_sync();
+  __syncthreads();
+  tc::fence_after_sync();
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp == 0) {
+    // ---- TMA producer ---------------------------------------------------------------
+    if (lane == 0) {
+      tma::prefetch_map(&w_map);
+      tma::prefetch_map(&x_map);
+      for (int i = 0; i < n_kb; ++i) {
+        const int stage = i % C::kStages;
+        if (i >= C::kStages &&
+            !tma::mbar_wait(&empty[stage], ((i / C::kStages) - 1) & 1, p.error, 301))
+          break;
+        uint8_t* dst = smem + stage * C::kStageBytes;
+        const int x = (kb0 + i) * BK;
+        tma::mbar_expect_tx(&full[stage], C::kStageBytes);
+        tma::load_2d(dst, &w_map, x, n0, &full[stage]);
+        if (kDual) tma::load_2d(dst + kWTile, &w_map, x, p.dual_offset + n0, &full[stage]);
+        tma::load_2d(dst + (kDual ? 2 : 1) * kWTile, &x_map, x, m0, &full[stage]);
+      }
+    }
+  } else if (warp == 1) {
+    // ---- MMA issue ------------------------------------------------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = tc::idesc_bf16_f32(BM, MT);
+      bool ok = true;
+      for (int i = 0; i < n_kb && ok; ++i) {
+        const int stage = i % C::kStages;
+        ok = tma::mbar_wait(&full[stage], (i / C::kStages) & 1, p.error, 302);
+        if (!ok) break;
+        tc::fence_after_sync();
+        const uint32_t a = tma::smem_u32(smem + stage * C::kStageBytes);
+        const uint32_t b = a + (kDual ? 2 : 1) * kWTile;
+#pragma unroll
+        for (int k = 0; k < BK / 16; ++k) {
+          const uint64_t bd = tc::smem_desc_k_major_sw128(b + k * 32);
+          tc::mma_ss(tmem, tc::smem_desc_k_major_sw128(a + k * 32), bd, idesc, i > 0 || k > 0);
+          if (kDual)
+            tc::mma_ss(tmem + MT, tc::smem_desc_k_major_sw128(a + kWTile + k * 32), bd, idesc,
+                       i > 0 || k > 0);
+        }
+        tc::commit(&empty[stage]);      // the stage is free once these MMAs have read it
+      }
+      tc::commit(accum);                // the accumulator is complete
+    }
+  } else {
+    // ---- epilogue: warp w reads the lanes of quarter w % 4 ------------------------------
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;          // lane of tensor memory = weight row in the tile
+    const int n = n0 + row;
+    const bool ok = tma::mbar_wait(accum, 0, p.error, 303);
+    tc::fence_after_sync();
+    const uint32_t taddr = tmem + (static_cast<uint32_t>(quarter * 32) << 16);
+    const float bias = bias_at(p, n);
+    if (p.splits == 1) {
+      if (ok) {
+#pragma unroll 1
+        for (int c = 0; c < MT; c += 16) {
+          float v[16], u[16];
+          tc::ld_32x32b_x16(taddr + c, v);
+          if (kDual) tc::ld_32x32b_x16(taddr + MT + c, u);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) finish(p, m0 + c + j, n, v[j], kDual ? u[j] : 0.f, bias);
+        }
+      }
+    } else {
+      const int tile = m_tile * gridDim.x + n_tile;
+      float* mine = p.partial + ((long long)tile * p.splits + split) * (C::kAcc * BM);
+      if (ok) {
+#pragma unroll 1
+        for (int c = 0; c < C::kAcc; c += 16) {
+          float v[16];
+          tc::ld_32x32b_x16(taddr + c, v);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) __stcg(mine + (c + j) * BM + row, v[j]);
+        }
+      }
+      __threadfence();
+      asm volatile("bar.sync 1, 128;");
+      if (threadIdx.x == 64) *last_flag = atomicAdd(p.tickets + tile, 1) == p.splits - 1;
+      asm volatile("bar.sync 1, 128;");
+      if (*last_flag) {
+        __threadfence();
+        const float* all = p.partial + (long long)tile * p.splits * (C::kAcc * BM);
+#pragma unroll 1
+        for (int c = 0; c < MT; ++c) {
+          if (m0 + c >= p.M) break;
+          float acc = 0.f, up = 0.f;
+          for (int s = 0; s < p.splits; ++s) {
+            acc += __ldcg(all + ((long long)s * C::kAcc + c) * BM + row);
+            if (kDual) up += __ldcg(all + ((long long)s * C::kAcc + MT + c) * BM + row);
+          }
+          finish(p, m0 + c, n, acc, up, bias);
+        }
+        if (threadIdx.x == 64) p.tickets[tile] = 0;     // ready for the next launch
+      }
+    }
+    tc::fence_before_sync();
+  }
+  __syncthreads();
+  if (warp == 1) {
+    tc::fence_after_sync();
+    tc::tmem_dealloc(tmem, C::kTmemCols);
+  }
+}
+
+__device__ int g_error;
+
+template <int MT, bool kDual>
+int launch(const CUtensorMap* w_map, const CUtensorMap* x_map, Params p, int n_tiles, int m_tiles,
+           cudaStream_t stream) {
+  using C = Cfg<MT, kDual>;
+  static bool configured = false;
+  if (!configured) {
+    const cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<MT, kDual>,
+                                               cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               C::kSmemBytes);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    configured = true;
+  }
+  if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p.error), g_error) != cudaSuccess)
+    return cudaErrorInvalidValue;
+  const dim3 grid(n_tiles, m_tiles, p.splits);
+  gemm_tc_kernel<MT, kDual><<<grid, kThreads, C::kSmemBytes, stream>>>(*w_map, *x_map, p);
+  return launch_status();
+}
+
+}  // namespace
+
+// A TMA descriptor of a row-major bf16 matrix [rows, cols] read in boxes of
+// [box_rows, 64 columns]; `map` points to 128 bytes on the host.
+SAKV_EXPORT int sakv_gemm_tc_map(void* map, const void* base, long long rows, long long cols,
+                                 long long row_stride_elems, int box_rows) {
+  if (rows <= 0 || cols <= 0 || (cols % 8) || (row_stride_elems % 8) || box_rows <= 0 ||
+      box_rows > 256)
+    return cudaErrorInvalidValue;
+  return tma::make_map_bf16_2d(reinterpret_cast<CUtensorMap*>(map), base, (uint64_t)rows,
+                               (uint64_t)cols, (uint64_t)row_stride_elems * 2, box_rows, BK);
+}
+
+// Floats of scratch and number of tickets that a launch with these sizes needs.
+SAKV_EXPORT long long sakv_gemm_tc_scratch(int mt, int dual, int n_tiles, int m_tiles, int splits) {
+  if (splits <= 1) return 0;
+  return (long long)n_tiles * m_tiles * splits * (dual ? 2 : 1) * mt * BM;
+}
+
+SAKV_EXPORT int sakv_gemm_tc(const void* w_map, const void* x_map, int M, int N, int K, int mt,
+                             int splits, int epi, int dual_offset, const void* bias,
+                             int bias_dtype, void* out, long long ldo, float* partial,
+                             int* tickets, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0 || (K % 8) || splits < 1 || epi < 0 || epi > EPI_GATED ||
+      ldo < N)
+    return cudaErrorInvalidValue;
+  const int total_kb = (K + BK - 1) / BK;
+  if (splits > total_kb) splits = total_kb;
+  Params p;
+  p.M = M; p.N = N; p.K = K;
+  p.kb_per_split = (total_kb + splits - 1) / splits;
+  p.splits = (total_kb + p.kb_per_split - 1) / p.kb_per_split;     // no empty split
+  p.dual_offset = dual_offset;
+  p.epi = epi; p.bias = bias; p.bias_dtype = bias_dtype;
+  p.out = out; p.ldo = ldo; p.partial = partial; p.tickets = tickets; p.error = nullptr;
+  if (p.splits > 1 && (!partial || !tickets)) return cudaErrorInvalidValue;
+  const int n_tiles = (N + BM - 1) / BM;
+  const int m_tiles = (M + mt - 1) / mt;
+  if (m_tiles > 65535 || p.splits > 65535) return cudaErrorInvalidValue;
+  const bool dual = epi == EPI_GATED;
+  const CUtensorMap* wm = (const CUtensorMap*)w_map;
+  const CUtensorMap* xm = (const CUtensorMap*)x_map;
+#define GO(MT_)                                                                   \
+  if (mt == MT_)                                                                  \
+    return dual ? launch<MT_, true>(wm, xm, p, n_tiles, m_tiles, stream)          \
+                : launch<MT_, false>(wm, xm, p, n_tiles, m_tiles, stream)
+  GO(16); GO(32); GO(64); GO(128);
+  if (mt == 256 && !dual) return launch<256, false>(wm, xm, p, n_tiles, m_tiles, stream);
+#undef GO
+  return cudaErrorInvalidValue;
+}
+
+// The number of splits this launch will really use (the host sizes the scratch with it).
+SAKV_EXPORT int sakv_gemm_tc_splits(int K, int splits) {
+  const int total_kb = (K + BK - 1) / BK;
+  if (splits > total_kb) splits = total_kb;
+  if (splits < 1) splits = 1;
+  const int per = (total_kb + splits - 1) / splits;
+  return (total_kb + per - 1) / per;
+}
+
+SAKV_EXPORT int sakv_gemm_tc_error(int* value) {
+  return static_cast<int>(cudaMemcpyFromSymbol(value, g_error, sizeof(int)));
+}

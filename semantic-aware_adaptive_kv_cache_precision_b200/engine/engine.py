@@ -42,7 +42,7 @@ class Engine:
     def __init__(self, model_dir=None, *, config=None, dtype: str = "bfloat16",
                  max_tokens: int = DEFAULT_MAX_TOKENS, max_batch: int = DEFAULT_MAX_BATCH,
                  max_step_tokens: int = DEFAULT_MAX_STEP_TOKENS, random_seed: int | None = None,
-                 device="cuda", poison_freed: bool = False):
+                 device="cuda", poison_freed: bool = False, cuda_graphs: bool = True):
         if not torch.cuda.is_available():
             raise RuntimeError("no CUDA device: this library runs its own sm_100a kernels "
                                "and has no CPU implementation")
@@ -63,6 +63,13 @@ class Engine:
         self.model = DecoderModel(self.spec, self.dtype, self.device)
         self.cache: SequenceCache | None = None
         self._stager = StepStager(self.device)
+        #: decode steps (one token per sequence, logits wanted for each) are captured in a
+        #: CUDA graph per batch shape and replayed: the step's integers live at fixed
+        #: device addresses, so a replay needs only the one copy that refreshes them
+        self.cuda_graphs = cuda_graphs
+        self._graphs: dict = {}
+        self._graph_pool = None
+        self._decode_ran_eagerly = False
         self.ending = None
         self.endings: list = []
         self._loaded = False
@@ -156,12 +163,37 @@ class Engine:
         with torch.cuda.device(self.device):
             cache.reserve(slots, ends)
             ctx = self._stager.build(slots, new_tokens, starts, rows, cache.tables_for(slots))
-            x = self.model.hidden(ctx, cache)
+            if self.cuda_graphs and ctx.is_decode and rows == list(range(len(slots))):
+                logits = self._decode_by_graph(ctx, cache)
+            else:
+                x = self.model.hidden(ctx, cache)
+                logits = self.model.logits(x, ctx.want) if rows else torch.empty(
+                    (0, self.spec.vocab_size), dtype=torch.float32, device=self.device)
             cache.advance(slots, ends)
-            if not rows:
-                return torch.empty((0, self.spec.vocab_size), dtype=torch.float32,
-                                   device=self.device)
-            return self.model.logits(x, ctx.want)
+            return logits
+
+    def _decode_by_graph(self, ctx, cache) -> torch.Tensor:
+        """Run a decode step through the CUDA graph of its shape (batch size and width of
+        the block lists), capturing it the first time the shape comes up after one
+        decode step has run eagerly (which loads and configures every kernel)."""
+        if not self._decode_ran_eagerly:
+            self._decode_ran_eagerly = True
+            return self.model.logits(self.model.hidden(ctx, cache), ctx.want)
+        key = (ctx.sequences, tuple(tuple(t.shape) for t in ctx.tables), self._stager.generation)
+        entry = self._graphs.get(key)
+        if entry is None:
+            if len(self._graphs) >= 64:                 # shapes come and go; keep the table small
+                self._graphs.clear()
+            graph = torch.cuda.CUDAGraph()
+            if self._graph_pool is None:
+                self._graph_pool = torch.cuda.graph_pool_handle()
+            torch.cuda.synchronize(self.device)
+            with torch.cuda.graph(graph, pool=self._graph_pool):
+                out = self.model.logits(self.model.hidden(ctx, cache), ctx.want)
+            entry = (graph, out)
+            self._graphs[key] = entry
+        entry[0].replay()
+        return entry[1].clone()
 
     # -- whole sequences ---------------------------------------------------------------
 

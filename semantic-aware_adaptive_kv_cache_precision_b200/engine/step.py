@@ -41,6 +41,7 @@ class StepContext:
     max_new: int = 0
     max_len: int = 0
     is_decode: bool = False           # every sequence brings exactly one token
+    max_len_bound: int = 0            # a bound on max_len that changes rarely (block-list width)
     q_tiles: torch.Tensor | None = None   # int32 [n, 4]: (sequence, first row, rows, first position)
 
 
@@ -53,11 +54,13 @@ class StepStager:
         self.host = self.dev = None
         self.copied = None
         self.last_bytes = 0
+        self.generation = 0
 
     def _ensure(self, count: int) -> None:
         if count <= self.capacity:
             return
-        self.capacity = max(1024, 2 * count)
+        self.capacity = max(1 << 18, 2 * count)
+        self.generation += 1                 # device addresses change: captured graphs are stale
         self.host = torch.empty(self.capacity, dtype=torch.int32, pin_memory=True)
         self.dev = torch.empty(self.capacity, dtype=torch.int32, device=self.device)
         self.copied = None
@@ -73,7 +76,9 @@ class StepStager:
         W = want_rows.size
         # block lists only as wide as the longest sequence of the step needs
         ends = [s + c for s, c in zip(starts, counts)]
-        width = max(1, -(-max(ends, default=1) // QUERY_TILE))
+        # (rounded up to a multiple of 8 blocks, so that a decode loop keeps one shape for
+        # 512 steps and its captured graph can be replayed)
+        width = -(-max(1, -(-max(ends, default=1) // QUERY_TILE)) // 8) * 8
         tables = [np.ascontiguousarray(t[:, :min(width, t.shape[1])]) for t in tables]
         # query tiles of up to 64 tokens, none crossing a sequence's end
         tiles, row = [], 0
@@ -127,4 +132,5 @@ class StepStager:
             tables=dev_tables, new_counts=counts, starts=list(starts), host_slots=list(slots),
             max_position=max(ends) - 1 if ends else 0, max_new=max(counts, default=0),
             max_len=max(ends, default=0), is_decode=all(c == 1 for c in counts),
+            max_len_bound=min(width, max((t.shape[1] for t in tables), default=width)) * QUERY_TILE,
             q_tiles=view("q_tiles", 4 * len(tiles)).view(len(tiles), 4))

@@ -11,13 +11,14 @@ from __future__ import annotations
 import torch
 
 from ._lib import BF16, CACHE_BLOCK, F32, KernelError, call, dtype_code, ptr, require_cuda
-from .linear import linear
+from .linear import gated_up, linear
+from . import gemm_tc
 from .attention import (attention_decode, attention_prefill, decode_splits, fast_path_takes,
                         kernel_errors)
 
 __all__ = ["CACHE_BLOCK", "KernelError", "embed", "rms_norm", "rope_store", "attention_plain",
            "attention_decode", "attention_prefill", "decode_splits", "fast_path_takes",
-           "kernel_errors", "gated_silu", "add_into", "linear", "choose"]
+           "kernel_errors", "gated_silu", "gated_up", "gemm_tc", "add_into", "linear", "choose"]
 
 
 def _check(cond: bool, message: str) -> None:

@@ -34,6 +34,7 @@ SIGNATURES = {
                               [P, P, P, L, P, P, I, P, P, P, I, I, I, I, I, F, I, P]),
     "sakv_prefill_attention": ("attention_prefill",
                                [P, P, P, L, P, P, I, P, P, I, I, I, I, F, I, P]),
+    "sakv_gemm_tc": ("gemm_tc", [P, P, I, I, I, I, I, I, I, P, I, P, L, P, P, P]),
 }
 
 #: functions without a stream argument: (library, argument types)
@@ -41,6 +42,10 @@ PLAIN_SIGNATURES = {
     "sakv_decode_attention_map": ("attention_decode", [P, P, L, I, I]),
     "sakv_decode_attention_error": ("attention_decode", [P]),
     "sakv_prefill_attention_error": ("attention_prefill", [P]),
+    "sakv_gemm_tc_map": ("gemm_tc", [P, P, L, L, L, I]),
+    "sakv_gemm_tc_scratch": ("gemm_tc", [I, I, I, I, I]),
+    "sakv_gemm_tc_splits": ("gemm_tc", [I, I]),
+    "sakv_gemm_tc_error": ("gemm_tc", [P]),
 }
 
 _functions: dict[str, object] = {}
@@ -63,7 +68,7 @@ def plain_function(name: str):
         library, argtypes = PLAIN_SIGNATURES[name]
         fn = getattr(_build.load(library), name)
         fn.argtypes = argtypes
-        fn.restype = c_int
+        fn.restype = c_longlong if name == "sakv_gemm_tc_scratch" else c_int
         _functions[name] = fn
     return fn
 

@@ -1,0 +1,104 @@
+"""Host side of the tcgen05 matrix product (`csrc/gemm_tc.cu`): TMA descriptors,
+tile and split choice, scratch for the splits."""
+
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from ._lib import BF16, F32, KernelError, call, dtype_code, plain_function, ptr
+
+SM_COUNT = 148
+EPI_BF16, EPI_F32, EPI_ACCUM, EPI_GATED = 0, 1, 2, 3
+
+_weight_maps: dict = {}
+_scratch: dict = {}           # device -> (partial, tickets); kept alive, captured graphs point here
+_retired: list = []
+
+
+def takes(x: torch.Tensor, weight: torch.Tensor) -> bool:
+    """Whether the tensor-core kernel takes these operands: bf16, K-major rows whose
+    strides are multiples of 16 bytes, 16-byte aligned bases."""
+    return (x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.dim() == 2
+            and weight.dim() == 2 and x.shape[1] == weight.shape[1] and x.shape[1] % 8 == 0
+            and x.stride(1) == 1 and x.stride(0) % 8 == 0 and weight.is_contiguous()
+            and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0 and x.shape[0] > 0)
+
+
+def _make_map(t: torch.Tensor, box_rows: int):
+    raw = ctypes.create_string_buffer(128 + 64)
+    address = (ctypes.addressof(raw) + 63) & ~63
+    code = plain_function("sakv_gemm_tc_map")(address, t.data_ptr(), t.shape[0], t.shape[1],
+                                              t.stride(0), box_rows)
+    if code != 0:
+        raise KernelError(f"could not make a TMA descriptor for a {tuple(t.shape)} matrix "
+                          f"(error {code})")
+    return raw, address
+
+
+def _weight_map(weight: torch.Tensor) -> int:
+    key = (weight.data_ptr(), tuple(weight.shape))
+    hit = _weight_maps.get(key)
+    if hit is None:
+        hit = _make_map(weight, 128)
+        _weight_maps[key] = hit
+    return hit[1]
+
+
+def token_tile(m: int, dual: bool) -> int:
+    for mt in (16, 32, 64, 128):
+        if m <= mt:
+            return mt
+    return 128 if dual else 256
+
+
+def choose_splits(n_tiles: int, m_tiles: int, k: int) -> int:
+    """Split K so that about one block per SM is busy; none when the tiles alone fill
+    most of the GPU."""
+    tiles = n_tiles * m_tiles
+    if tiles * 4 >= SM_COUNT * 3:
+        return 1
+    total_kb = -(-k // 64)
+    want = max(1, min(total_kb, SM_COUNT // tiles))
+    return plain_function("sakv_gemm_tc_splits")(k, want)
+
+
+def _scratch_for(device, floats: int, tiles: int):
+    have = _scratch.get(device)
+    if have is None or have[0].numel() < floats or have[1].numel() < tiles:
+        if have is not None:
+            _retired.append(have)            # graphs captured earlier may still use it
+        partial = torch.empty(max(floats, 1 << 22), dtype=torch.float32, device=device)
+        tickets = torch.zeros(max(tiles, 4096), dtype=torch.int32, device=device)
+        have = (partial, tickets)
+        _scratch[device] = have
+    return have
+
+
+def gemm(x: torch.Tensor, weight: torch.Tensor, bias, epi: int, out: torch.Tensor,
+         n: int, dual_offset: int = 0, splits: int | None = None) -> torch.Tensor:
+    """`out` is written (EPI_BF16, EPI_F32, EPI_GATED) or added to (EPI_ACCUM); `n` is the
+    number of output columns (rows of `weight`, or half of them for EPI_GATED)."""
+    m, k = x.shape
+    dual = epi == EPI_GATED
+    mt = token_tile(m, dual)
+    n_tiles, m_tiles = -(-n // 128), -(-m // mt)
+    if splits is None:
+        splits = choose_splits(n_tiles, m_tiles, k)
+    splits = plain_function("sakv_gemm_tc_splits")(k, splits)
+    partial = tickets = None
+    if splits > 1:
+        floats = plain_function("sakv_gemm_tc_scratch")(mt, int(dual), n_tiles, m_tiles, splits)
+        partial, tickets = _scratch_for(x.device, floats, n_tiles * m_tiles)
+    x_raw, x_map = _make_map(x, mt)
+    call("sakv_gemm_tc", _weight_map(weight), x_map, m, n, k, mt, splits, epi, dual_offset,
+         ptr(bias), dtype_code(bias.dtype) if bias is not None else BF16, ptr(out),
+         out.stride(0), ptr(partial), ptr(tickets))
+    return out
+
+
+def error_word() -> int:
+    value = ctypes.c_int(0)
+    code = plain_function("sakv_gemm_tc_error")(ctypes.addressof(value))
+    return value.value if code == 0 else -code

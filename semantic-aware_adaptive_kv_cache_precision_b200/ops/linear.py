@@ -15,7 +15,23 @@ from __future__ import annotations
 
 import torch
 
+from . import gemm_tc
 from ._lib import KernelError, call, ptr, require_cuda
+
+#: up to this many tokens the library's own tcgen05 kernel runs; above it, cuBLAS
+TC_MAX_TOKENS = 256
+
+
+def gated_up(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
+    """`silu(x Wgate^T) * (x Wup^T)` for `w_gate_up = [Wgate; Wup]`: one kernel with the
+    activation in its epilogue where the tensor-core kernel takes the operands, else the
+    product followed by the activation kernel."""
+    from . import gated_silu
+    inter = w_gate_up.shape[0] // 2
+    if x.shape[0] <= TC_MAX_TOKENS and inter % 128 == 0 and gemm_tc.takes(x, w_gate_up):
+        out = torch.empty((x.shape[0], inter), dtype=torch.bfloat16, device=x.device)
+        return gemm_tc.gemm(x, w_gate_up, None, gemm_tc.EPI_GATED, out, inter, dual_offset=inter)
+    return gated_silu(linear(x, w_gate_up, out_dtype=x.dtype))
 
 
 def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None, *,
@@ -54,6 +70,16 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = No
     if weight.dtype != torch.bfloat16:
         raise KernelError(f"linear: weight type {weight.dtype} is not supported")
     xb = x if x.dtype == torch.bfloat16 else x.to(torch.bfloat16)
+    if tokens <= TC_MAX_TOKENS and gemm_tc.takes(xb, weight) and \
+            (bias is None or bias.dtype in (torch.bfloat16, torch.float32)):
+        if accumulate_into is not None:
+            return gemm_tc.gemm(xb, weight, bias, gemm_tc.EPI_ACCUM, acc, n)
+        if out_dtype == torch.float32:
+            out = torch.empty((tokens, n), dtype=torch.float32, device=x.device)
+            return gemm_tc.gemm(xb, weight, bias, gemm_tc.EPI_F32, out, n)
+        if out_dtype == torch.bfloat16:
+            out = torch.empty((tokens, n), dtype=torch.bfloat16, device=x.device)
+            return gemm_tc.gemm(xb, weight, bias, gemm_tc.EPI_BF16, out, n)
     if accumulate_into is not None:
         from . import add_into
         y = torch.mm(xb, weight.t(), out_dtype=torch.float32)

@@ -92,7 +92,7 @@ class GQAAttention(Part):
             if step.is_decode:
                 return ops.attention_decode(qkv, view.keys, view.values, step.seq_lens,
                                             view.block_table, s.heads, s.kv_heads, s.head_dim,
-                                            s.scale, s.window, step.max_len)
+                                            s.scale, s.window, step.max_len_bound or step.max_len)
             return ops.attention_prefill(qkv, view.keys, view.values, step.q_tiles,
                                          step.seq_lens, view.block_table, s.heads, s.kv_heads,
                                          s.head_dim, s.scale, s.window)

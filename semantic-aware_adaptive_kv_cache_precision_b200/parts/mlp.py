@@ -35,8 +35,7 @@ class GatedMLP(Part):
         self.w_down = arena.view(p + "down_proj.weight")
 
     def forward(self, h, step, residual):
-        gate_up = ops.linear(h, self.w_gate_up, out_dtype=self.act_dtype)
-        act = ops.gated_silu(gate_up)
+        act = ops.gated_up(h, self.w_gate_up)
         ops.linear(act, self.w_down, accumulate_into=residual)
 
 

@@ -471,3 +471,58 @@ def test_tensor_core_attention_finds_one_far_key(kernel):
             np.testing.assert_allclose(out[h], want, rtol=0, atol=2e-2,
                                        err_msg=f"{kernel}: far key at {far}, head {h}")
         assert np.abs(out[0] - want).max() > 0.1
+
+
+# ---- the tcgen05 matrix product -----------------------------------------------------------
+
+@pytest.mark.parametrize("M,N,K", [(1, 128, 64), (8, 1536, 1536), (8, 2048, 1536), (16, 70, 72),
+                                   (17, 1000, 352), (64, 1536, 8960), (100, 384, 200),
+                                   (256, 640, 1536), (3, 151936 // 8, 256)])
+@pytest.mark.parametrize("splits", [None, 1, 3])
+def test_gemm_tc_epilogues(M, N, K, splits):
+    from semantic_aware_adaptive_kv_cache_precision_b200.ops import gemm_tc
+    rng = np.random.default_rng(M + N + K)
+    x = dev(rng.standard_normal((M, K)), torch.bfloat16)
+    w = dev(rng.standard_normal((N, K)), torch.bfloat16)
+    b = dev(rng.standard_normal(N), torch.bfloat16)
+    assert gemm_tc.takes(x, w)
+    want = host(x) @ host(w).T
+    scale = np.abs(want).max()
+    out32 = torch.empty((M, N), dtype=torch.float32, device=DEV)
+    gemm_tc.gemm(x, w, None, gemm_tc.EPI_F32, out32, N, splits=splits)
+    assert gemm_tc.error_word() == 0
+    assert np.abs(host(out32) - want).max() <= 2e-6 * scale * np.sqrt(K) + 1e-6
+    out16 = torch.empty((M, N), dtype=torch.bfloat16, device=DEV)
+    gemm_tc.gemm(x, w, b, gemm_tc.EPI_BF16, out16, N, splits=splits)
+    assert np.abs(host(out16) - (want + host(b))).max() <= 2.0 ** -8 * (scale + 4)
+    acc = dev(rng.standard_normal((M, N)))
+    before = host(acc)
+    gemm_tc.gemm(x, w, None, gemm_tc.EPI_ACCUM, acc, N, splits=splits)
+    gemm_tc.gemm(x, w, None, gemm_tc.EPI_ACCUM, acc, N, splits=splits)      # tickets reset themselves
+    assert np.abs(host(acc) - (before + 2 * want)).max() <= 4e-6 * scale * np.sqrt(K) + 1e-5
+    assert gemm_tc.error_word() == 0
+
+
+@pytest.mark.parametrize("M,I,K", [(1, 128, 64), (8, 8960, 1536), (50, 256, 200), (128, 384, 1536)])
+def test_gemm_tc_gated(M, I, K):
+    rng = np.random.default_rng(M + I + K)
+    x = dev(rng.standard_normal((M, K)) * 0.5, torch.bfloat16)
+    w = dev(rng.standard_normal((2 * I, K)) * 0.2, torch.bfloat16)
+    got = ops.gated_up(x, w)
+    assert got.shape == (M, I) and got.dtype == torch.bfloat16
+    g = host(x) @ host(w[:I]).T
+    u = host(x) @ host(w[I:]).T
+    want = g / (1 + np.exp(-g)) * u
+    assert np.abs(host(got) - want).max() <= 2.0 ** -7 * np.abs(want).max() + 1e-3
+    two_step = ops.gated_silu(ops.linear(x, w, out_dtype=torch.bfloat16))
+    assert np.abs(host(got) - host(two_step)).max() <= 2.0 ** -6 * np.abs(want).max() + 1e-3
+
+
+def test_gemm_tc_refuses_what_it_cannot_take():
+    from semantic_aware_adaptive_kv_cache_precision_b200.ops import gemm_tc
+    x = torch.zeros((4, 36), dtype=torch.bfloat16, device=DEV)        # K not a multiple of 8
+    w = torch.zeros((128, 36), dtype=torch.bfloat16, device=DEV)
+    assert not gemm_tc.takes(x, w)
+    out = ops.linear(x, w)                                            # the library product runs
+    assert out.shape == (4, 128)
+    assert not gemm_tc.takes(x.float(), w)
