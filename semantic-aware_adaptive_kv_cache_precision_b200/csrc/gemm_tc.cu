@@ -17,11 +17,13 @@
 //                                                      matrix, two accumulators side by side
 //
 // With few tokens and a small N there are too few row tiles to fill 148 SMs, so K is
-// split over blockIdx.z: every split writes its partial tile to scratch, takes a
-// ticket, and the last one adds the partials in split order (the same order every
-// time) and runs the epilogue. The reference calls cuBLAS for all of this
-// (`src/core_kernels/linear.cu:85-142`); warps: 0 = TMA, 1 = MMA issue and tensor
-// memory, 2..5 = epilogue. No cluster multicast anywhere.
+// split over the blocks of a thread-block cluster (up to 8, along blockIdx.z): every
+// block leaves its partial tile in its own shared memory, the cluster synchronises,
+// and each block then finishes a share of the token columns by adding the partials of
+// all blocks in rank order (the same order every time) through distributed shared
+// memory. Nothing goes through global scratch. The reference calls cuBLAS for all of
+// this (`src/core_kernels/linear.cu:85-142`); warps: 0 = TMA, 1 = MMA issue and tensor
+// memory, 2..5 = epilogue. TMA loads are plain per-block loads, never cluster multicast.
 #include "common.cuh"
 #include "tcgen05.cuh"
 #include "tma.cuh"
@@ -32,21 +34,20 @@ constexpr int BM = 128;          // weight rows per block (MMA M)
 constexpr int BK = 64;           // columns per stage (one 128-byte swizzle row)
 constexpr int kThreads = 192;
 constexpr int kWTile = BM * BK * 2;
-constexpr int kSmemBudget = 200 * 1024;
+constexpr int kMaxSplits = 8;     // portable cluster size
 
 enum : int { EPI_BF16 = 0, EPI_F32 = 1, EPI_ACCUM = 2, EPI_GATED = 3 };
 
 struct Params {
   int M, N, K;
   int splits, kb_per_split;
+  int stages;            // tiles in flight per block (ring of shared-memory stages)
   int dual_offset;       // row of W where the "up" half starts (gated_silu)
   int epi;
   const void* bias;      // [N] or null
   int bias_dtype;
   void* out;             // [M, ldo]
   long long ldo;
-  float* partial;        // scratch of the splits
-  int* tickets;          // one counter per tile, zero before and after every launch
   int* error;
 };
 
@@ -54,13 +55,41 @@ template <int MT, bool kDual>
 struct Cfg {
   static constexpr int kXTile = MT * BK * 2;
   static constexpr int kStageBytes = (kDual ? 2 : 1) * kWTile + kXTile;
-  static constexpr int kStagesRaw = kSmemBudget / kStageBytes;
-  static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
+  static constexpr int kMaxStages = 10;
   static constexpr int kAcc = (kDual ? 2 : 1) * MT;
+  static constexpr int kPartialBytes = kAcc * BM * 4;     // the split partial reuses the stages
+  // With one block per SM (a grid that fits the GPU in one wave) a block takes as many
+  // stages as fit, to keep enough bytes in flight; with several waves it takes fewer, so
+  // that two or three blocks share an SM and one's epilogue overlaps another's streaming.
+  static int stages_for(long long blocks) {
+    const int budget = blocks <= 148 ? 200 * 1024
+                       : MT <= 32 ? (kDual ? 104 : 72) * 1024
+                       : MT == 64 ? (kDual ? 160 : 100) * 1024 : 200 * 1024;
+    int s = budget / kStageBytes;
+    if (s > kMaxStages) s = kMaxStages;
+    while (s * kStageBytes < kPartialBytes) ++s;
+    return s < 2 ? 2 : s;
+  }
+  static int smem_bytes(int stages) { return stages * kStageBytes + 1024 + 256; }
   static constexpr int kTmemCols = kAcc <= 32 ? 32 : kAcc <= 64 ? 64 : kAcc <= 128 ? 128
                                    : kAcc <= 256 ? 256 : 512;
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
 };
+
+__device__ __forceinline__ void cluster_sync_all() {
+  __syncwarp();      // the single-lane roles of warps 0 and 1 have to be back with their warps
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// The value at shared-memory address `local` (of this block's window) in the block of
+// rank `rank` of the cluster.
+__device__ __forceinline__ float ld_peer(uint32_t local, uint32_t rank) {
+  uint32_t remote;
+  float v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(rank));
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+  return v;
+}
 
 __device__ __forceinline__ float bias_at(const Params& p, int n) {
   if (!p.bias || n >= p.N) return 0.f;
@@ -92,11 +121,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~uintptr_t(1023));
-  uint64_t* full = reinterpret_cast<uint64_t*>(smem + C::kStages * C::kStageBytes);
-  uint64_t* empty = full + C::kStages;
-  uint64_t* accum = empty + C::kStages;
+  const int stages = p.stages;
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + stages * C::kStageBytes);
+  uint64_t* empty = full + stages;
+  uint64_t* accum = empty + stages;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum + 1);
-  int* last_flag = reinterpret_cast<int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_tile = blockIdx.x, m_tile = blockIdx.y, split = blockIdx.z;
@@ -107,7 +136,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
   const int n_kb = kb1 - kb0;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < C::kStages; ++s) {
+    for (int s = 0; s < stages; ++s) {
       tma::mbar_init(&full[s], 1);
       tma::mbar_init(&empty[s], 1);
     }
@@ -126,9 +155,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
       tma::prefetch_map(&w_map);
       tma::prefetch_map(&x_map);
       for (int i = 0; i < n_kb; ++i) {
-        const int stage = i % C::kStages;
-        if (i >= C::kStages &&
-            !tma::mbar_wait(&empty[stage], ((i / C::kStages) - 1) & 1, p.error, 301))
+        const int stage = i % stages;
+        if (i >= stages &&
+            !tma::mbar_wait(&empty[stage], ((i / stages) - 1) & 1, p.error, 301))
           break;
         uint8_t* dst = smem + stage * C::kStageBytes;
         const int x = (kb0 + i) * BK;
@@ -144,8 +173,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
       constexpr uint32_t idesc = tc::idesc_bf16_f32(BM, MT);
       bool ok = true;
       for (int i = 0; i < n_kb && ok; ++i) {
-        const int stage = i % C::kStages;
-        ok = tma::mbar_wait(&full[stage], (i / C::kStages) & 1, p.error, 302);
+        const int stage = i % stages;
+        ok = tma::mbar_wait(&full[stage], (i / stages) & 1, p.error, 302);
         if (!ok) break;
         tc::fence_after_sync();
         const uint32_t a = tma::smem_u32(smem + stage * C::kStageBytes);
@@ -182,39 +211,48 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
           for (int j = 0; j < 16; ++j) finish(p, m0 + c + j, n, v[j], kDual ? u[j] : 0.f, bias);
         }
       }
-    } else {
-      const int tile = m_tile * gridDim.x + n_tile;
-      float* mine = p.partial + ((long long)tile * p.splits + split) * (C::kAcc * BM);
-      if (ok) {
+    } else if (ok) {
+      // this block's partial tile -> its own shared memory, [column][row] fp32
+      float* mine = reinterpret_cast<float*>(smem);
 #pragma unroll 1
-        for (int c = 0; c < C::kAcc; c += 16) {
-          float v[16];
-          tc::ld_32x32b_x16(taddr + c, v);
+      for (int c = 0; c < C::kAcc; c += 16) {
+        float v[16];
+        tc::ld_32x32b_x16(taddr + c, v);
 #pragma unroll
-          for (int j = 0; j < 16; ++j) __stcg(mine + (c + j) * BM + row, v[j]);
-        }
-      }
-      __threadfence();
-      asm volatile("bar.sync 1, 128;");
-      if (threadIdx.x == 64) *last_flag = atomicAdd(p.tickets + tile, 1) == p.splits - 1;
-      asm volatile("bar.sync 1, 128;");
-      if (*last_flag) {
-        __threadfence();
-        const float* all = p.partial + (long long)tile * p.splits * (C::kAcc * BM);
-#pragma unroll 1
-        for (int c = 0; c < MT; ++c) {
-          if (m0 + c >= p.M) break;
-          float acc = 0.f, up = 0.f;
-          for (int s = 0; s < p.splits; ++s) {
-            acc += __ldcg(all + ((long long)s * C::kAcc + c) * BM + row);
-            if (kDual) up += __ldcg(all + ((long long)s * C::kAcc + MT + c) * BM + row);
-          }
-          finish(p, m0 + c, n, acc, up, bias);
-        }
-        if (threadIdx.x == 64) p.tickets[tile] = 0;     // ready for the next launch
+        for (int j = 0; j < 16; ++j) mine[(c + j) * BM + row] = v[j];
       }
     }
     tc::fence_before_sync();
+  }
+  if (p.splits > 1) {
+    // Every thread of every block of the cluster comes here, whatever happened above.
+    cluster_sync_all();
+    if (warp >= 2) {
+      const int row = (warp & 3) * 32 + lane;
+      const int n = n0 + row;
+      const float bias = bias_at(p, n);
+      const uint32_t base = tma::smem_u32(smem);
+      // token columns split, split + splits, ... are finished by this block
+      for (int c = split; c < MT && m0 + c < p.M; c += p.splits) {
+        float part[kMaxSplits], part_up[kMaxSplits];
+#pragma unroll
+        for (int s = 0; s < kMaxSplits; ++s) {
+          part[s] = part_up[s] = 0.f;
+          if (s < p.splits) {
+            part[s] = ld_peer(base + (c * BM + row) * 4, s);
+            if (kDual) part_up[s] = ld_peer(base + ((MT + c) * BM + row) * 4, s);
+          }
+        }
+        float acc = 0.f, up = 0.f;
+#pragma unroll
+        for (int s = 0; s < kMaxSplits; ++s) {
+          acc += part[s];
+          up += part_up[s];
+        }
+        finish(p, m0 + c, n, acc, up, bias);
+      }
+    }
+    cluster_sync_all();       // nobody leaves while a peer may still read its shared memory
   }
   __syncthreads();
   if (warp == 1) {
@@ -233,15 +271,29 @@ int launch(const CUtensorMap* w_map, const CUtensorMap* x_map, Params p, int n_t
   if (!configured) {
     const cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<MT, kDual>,
                                                cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                               C::kSmemBytes);
+                                               C::smem_bytes(C::kMaxStages) > 227 * 1024
+                                                   ? 227 * 1024 : C::smem_bytes(C::kMaxStages));
     if (e != cudaSuccess) return static_cast<int>(e);
     configured = true;
   }
+  p.stages = C::stages_for((long long)n_tiles * m_tiles * p.splits);
+  while (C::smem_bytes(p.stages) > 227 * 1024) --p.stages;
   if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p.error), g_error) != cudaSuccess)
     return cudaErrorInvalidValue;
-  const dim3 grid(n_tiles, m_tiles, p.splits);
-  gemm_tc_kernel<MT, kDual><<<grid, kThreads, C::kSmemBytes, stream>>>(*w_map, *x_map, p);
-  return launch_status();
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(n_tiles, m_tiles, p.splits);
+  config.blockDim = dim3(kThreads);
+  config.dynamicSmemBytes = C::smem_bytes(p.stages);
+  config.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = p.splits;
+  config.attrs = attr;
+  config.numAttrs = 1;
+  const cudaError_t e = cudaLaunchKernelEx(&config, gemm_tc_kernel<MT, kDual>, *w_map, *x_map, p);
+  return e != cudaSuccess ? static_cast<int>(e) : launch_status();
 }
 
 }  // namespace
@@ -257,32 +309,25 @@ SAKV_EXPORT int sakv_gemm_tc_map(void* map, const void* base, long long rows, lo
                                (uint64_t)cols, (uint64_t)row_stride_elems * 2, box_rows, BK);
 }
 
-// Floats of scratch and number of tickets that a launch with these sizes needs.
-SAKV_EXPORT long long sakv_gemm_tc_scratch(int mt, int dual, int n_tiles, int m_tiles, int splits) {
-  if (splits <= 1) return 0;
-  return (long long)n_tiles * m_tiles * splits * (dual ? 2 : 1) * mt * BM;
-}
-
 SAKV_EXPORT int sakv_gemm_tc(const void* w_map, const void* x_map, int M, int N, int K, int mt,
                              int splits, int epi, int dual_offset, const void* bias,
-                             int bias_dtype, void* out, long long ldo, float* partial,
-                             int* tickets, cudaStream_t stream) {
+                             int bias_dtype, void* out, long long ldo, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0 || (K % 8) || splits < 1 || epi < 0 || epi > EPI_GATED ||
       ldo < N)
     return cudaErrorInvalidValue;
   const int total_kb = (K + BK - 1) / BK;
   if (splits > total_kb) splits = total_kb;
+  if (splits > kMaxSplits) splits = kMaxSplits;
   Params p;
   p.M = M; p.N = N; p.K = K;
   p.kb_per_split = (total_kb + splits - 1) / splits;
   p.splits = (total_kb + p.kb_per_split - 1) / p.kb_per_split;     // no empty split
   p.dual_offset = dual_offset;
   p.epi = epi; p.bias = bias; p.bias_dtype = bias_dtype;
-  p.out = out; p.ldo = ldo; p.partial = partial; p.tickets = tickets; p.error = nullptr;
-  if (p.splits > 1 && (!partial || !tickets)) return cudaErrorInvalidValue;
+  p.out = out; p.ldo = ldo; p.error = nullptr;
   const int n_tiles = (N + BM - 1) / BM;
   const int m_tiles = (M + mt - 1) / mt;
-  if (m_tiles > 65535 || p.splits > 65535) return cudaErrorInvalidValue;
+  if (m_tiles > 65535) return cudaErrorInvalidValue;
   const bool dual = epi == EPI_GATED;
   const CUtensorMap* wm = (const CUtensorMap*)w_map;
   const CUtensorMap* xm = (const CUtensorMap*)x_map;
@@ -296,10 +341,11 @@ SAKV_EXPORT int sakv_gemm_tc(const void* w_map, const void* x_map, int M, int N,
   return cudaErrorInvalidValue;
 }
 
-// The number of splits this launch will really use (the host sizes the scratch with it).
+// The number of splits a launch asked for `splits` will really use.
 SAKV_EXPORT int sakv_gemm_tc_splits(int K, int splits) {
   const int total_kb = (K + BK - 1) / BK;
   if (splits > total_kb) splits = total_kb;
+  if (splits > kMaxSplits) splits = kMaxSplits;
   if (splits < 1) splits = 1;
   const int per = (total_kb + splits - 1) / splits;
   return (total_kb + per - 1) / per;

@@ -28,23 +28,31 @@ __device__ __forceinline__ void keep_better(float& best, int& at, float value, i
   }
 }
 
+// One block scans one chunk of one row and leaves its best (value, index); the last
+// block of a row to finish (a ticket) picks the row's winner among the chunks. The
+// ticket counter is back at zero when the kernel ends.
+constexpr int kChunk = 8192;
+
 __global__ void choose_kernel(const float* __restrict__ logits, long long row_stride, int vocab,
                               float temperature, unsigned long long seed,
                               const int32_t* __restrict__ request,
-                              const int32_t* __restrict__ step, int32_t* __restrict__ out) {
+                              const int32_t* __restrict__ step, int32_t* __restrict__ out,
+                              float* __restrict__ chunk_best, int32_t* __restrict__ chunk_at,
+                              int32_t* __restrict__ tickets) {
   __shared__ float best_s[32];
   __shared__ int at_s[32];
-  const float* row = logits + (long long)blockIdx.x * row_stride;
+  __shared__ int last;
+  const int r = blockIdx.y, chunks = gridDim.x;
+  const float* row = logits + (long long)r * row_stride;
   unsigned long long key = 0;
   if (temperature > 0.f) {
-    key = splitmix64(seed + 0x9E3779B97F4A7C15ull *
-                                (unsigned long long)(unsigned)(request[blockIdx.x] + 1));
-    key = splitmix64(key ^ ((unsigned long long)(unsigned)step[blockIdx.x] *
-                            0xD1B54A32D192ED03ull));
+    key = splitmix64(seed + 0x9E3779B97F4A7C15ull * (unsigned long long)(unsigned)(request[r] + 1));
+    key = splitmix64(key ^ ((unsigned long long)(unsigned)step[r] * 0xD1B54A32D192ED03ull));
   }
   float best = -INFINITY;
   int at = vocab;
-  for (int c = threadIdx.x; c < vocab; c += blockDim.x) {
+  const int begin = blockIdx.x * kChunk, end = min(vocab, begin + kChunk);
+  for (int c = begin + threadIdx.x; c < end; c += blockDim.x) {
     float v = row[c];
     if (temperature > 0.f) {
       const unsigned long long z = splitmix64(key + (unsigned long long)c * 0x9E3779B97F4A7C15ull);
@@ -65,20 +73,52 @@ __global__ void choose_kernel(const float* __restrict__ logits, long long row_st
   if (threadIdx.x == 0) {
     const int warps = (blockDim.x + 31) >> 5;
     for (int w = 1; w < warps; ++w) keep_better(best_s[0], at_s[0], best_s[w], at_s[w]);
-    out[blockIdx.x] = at_s[0];
+    chunk_best[(long long)r * chunks + blockIdx.x] = best_s[0];
+    chunk_at[(long long)r * chunks + blockIdx.x] = at_s[0];
+    __threadfence();
+    last = atomicAdd(tickets + r, 1) == chunks - 1;
+  }
+  __syncthreads();
+  if (!last) return;
+  __threadfence();
+  best = -INFINITY;
+  at = vocab;
+  for (int c = threadIdx.x; c < chunks; c += blockDim.x)
+    keep_better(best, at, __ldcg(chunk_best + (long long)r * chunks + c),
+                __ldcg(chunk_at + (long long)r * chunks + c));
+  for (int o = 16; o > 0; o >>= 1)
+    keep_better(best, at, __shfl_down_sync(0xffffffffu, best, o),
+                __shfl_down_sync(0xffffffffu, at, o));
+  if (lane == 0) {
+    best_s[warp] = best;
+    at_s[warp] = at;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int warps = (blockDim.x + 31) >> 5;
+    for (int w = 1; w < warps; ++w) keep_better(best_s[0], at_s[0], best_s[w], at_s[w]);
+    out[r] = at_s[0];
+    tickets[r] = 0;
   }
 }
 
 }  // namespace
 
+// Scratch per row: one (value, index) pair per chunk of 8192 logits, and a ticket that is
+// zero between launches. `sakv_choose_chunks(vocab)` says how many chunks a row has.
+SAKV_EXPORT int sakv_choose_chunks(int vocab) { return (vocab + kChunk - 1) / kChunk; }
+
 SAKV_EXPORT int sakv_choose(const float* logits, long long row_stride, int rows, int vocab,
                             float temperature, unsigned long long seed, const int32_t* request,
-                            const int32_t* step, int32_t* out, cudaStream_t stream) {
-  if (rows < 0 || vocab <= 0 || row_stride < vocab || !(temperature >= 0.f))
+                            const int32_t* step, int32_t* out, float* chunk_best,
+                            int32_t* chunk_at, int32_t* tickets, cudaStream_t stream) {
+  if (rows < 0 || vocab <= 0 || row_stride < vocab || !(temperature >= 0.f) || !chunk_best ||
+      !chunk_at || !tickets || rows > 65535)
     return cudaErrorInvalidValue;
   if (temperature > 0.f && (!request || !step)) return cudaErrorInvalidValue;
   if (rows == 0) return 0;
-  choose_kernel<<<rows, 512, 0, stream>>>(logits, row_stride, vocab, temperature, seed, request,
-                                          step, out);
+  const dim3 grid((vocab + kChunk - 1) / kChunk, rows);
+  choose_kernel<<<grid, 256, 0, stream>>>(logits, row_stride, vocab, temperature, seed, request,
+                                          step, out, chunk_best, chunk_at, tickets);
   return launch_status();
 }

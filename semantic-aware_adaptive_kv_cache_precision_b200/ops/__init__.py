@@ -10,7 +10,8 @@ from __future__ import annotations
 
 import torch
 
-from ._lib import BF16, CACHE_BLOCK, F32, KernelError, call, dtype_code, ptr, require_cuda
+from ._lib import (BF16, CACHE_BLOCK, F32, KernelError, call, dtype_code, plain_function, ptr,
+                   require_cuda)
 from .linear import gated_up, linear
 from . import gemm_tc
 from .attention import (attention_decode, attention_prefill, decode_splits, fast_path_takes,
@@ -147,6 +148,18 @@ def choose(logits: torch.Tensor, temperature: float = 0.0, seed: int = 0,
             _check(t is not None and t.dtype == torch.int32 and t.is_contiguous()
                    and t.numel() == rows, f"{name}: int32 [rows]")
     out = torch.empty((rows,), dtype=torch.int32, device=logits.device)
+    chunks = plain_function("sakv_choose_chunks")(vocab)
+    scratch = _choose_scratch.get(logits.device)
+    if scratch is None or scratch[0].numel() < rows * chunks or scratch[2].numel() < rows:
+        size = max(rows * chunks, 4096)
+        scratch = (torch.empty(size, dtype=torch.float32, device=logits.device),
+                   torch.empty(size, dtype=torch.int32, device=logits.device),
+                   torch.zeros(max(rows, 1024), dtype=torch.int32, device=logits.device))
+        _choose_scratch[logits.device] = scratch
     call("sakv_choose", ptr(logits), logits.stride(0) if rows else vocab, rows, vocab,
-         float(temperature), int(seed) & 0xFFFFFFFFFFFFFFFF, ptr(request), ptr(step), ptr(out))
+         float(temperature), int(seed) & 0xFFFFFFFFFFFFFFFF, ptr(request), ptr(step), ptr(out),
+         ptr(scratch[0]), ptr(scratch[1]), ptr(scratch[2]))
     return out
+
+
+_choose_scratch: dict = {}

@@ -29,21 +29,21 @@ SIGNATURES = {
     "sakv_attention_plain": ("attention_plain",
                              [P, I, L, P, P, P, P, P, P, I, I, I, I, I, F, I, P]),
     "sakv_gemm_f32": ("gemm_f32", [P, L, P, P, P, L, I, I, I, I, P]),
-    "sakv_choose": ("sampling", [P, L, I, I, F, U, P, P, P, P]),
+    "sakv_choose": ("sampling", [P, L, I, I, F, U, P, P, P, P, P, P, P]),
     "sakv_decode_attention": ("attention_decode",
                               [P, P, P, L, P, P, I, P, P, P, I, I, I, I, I, F, I, P]),
     "sakv_prefill_attention": ("attention_prefill",
                                [P, P, P, L, P, P, I, P, P, I, I, I, I, F, I, P]),
-    "sakv_gemm_tc": ("gemm_tc", [P, P, I, I, I, I, I, I, I, P, I, P, L, P, P, P]),
+    "sakv_gemm_tc": ("gemm_tc", [P, P, I, I, I, I, I, I, I, P, I, P, L, P]),
 }
 
 #: functions without a stream argument: (library, argument types)
 PLAIN_SIGNATURES = {
+    "sakv_choose_chunks": ("sampling", [I]),
     "sakv_decode_attention_map": ("attention_decode", [P, P, L, I, I]),
     "sakv_decode_attention_error": ("attention_decode", [P]),
     "sakv_prefill_attention_error": ("attention_prefill", [P]),
     "sakv_gemm_tc_map": ("gemm_tc", [P, P, L, L, L, I]),
-    "sakv_gemm_tc_scratch": ("gemm_tc", [I, I, I, I, I]),
     "sakv_gemm_tc_splits": ("gemm_tc", [I, I]),
     "sakv_gemm_tc_error": ("gemm_tc", [P]),
 }
@@ -68,7 +68,7 @@ def plain_function(name: str):
         library, argtypes = PLAIN_SIGNATURES[name]
         fn = getattr(_build.load(library), name)
         fn.argtypes = argtypes
-        fn.restype = c_longlong if name == "sakv_gemm_tc_scratch" else c_int
+        fn.restype = c_int
         _functions[name] = fn
     return fn
 

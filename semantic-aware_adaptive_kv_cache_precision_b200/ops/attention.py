@@ -41,9 +41,9 @@ def tensor_map(cache: torch.Tensor):
 
 
 def decode_splits(sequences: int, kv_heads: int, max_len: int) -> int:
-    """How many ways to split the keys so that about two blocks per SM are busy."""
+    """How many ways to split the keys so that about one block per SM is busy."""
     tiles = max(1, -(-max_len // CACHE_BLOCK))
-    want = -(-2 * SM_COUNT // max(1, sequences * kv_heads))
+    want = max(1, SM_COUNT // max(1, sequences * kv_heads))
     return max(1, min(tiles, want, 32))
 
 

@@ -1,5 +1,5 @@
-"""Host side of the tcgen05 matrix product (`csrc/gemm_tc.cu`): TMA descriptors,
-tile and split choice, scratch for the splits."""
+"""Host side of the tcgen05 matrix product (`csrc/gemm_tc.cu`): TMA descriptors and the
+choice of token tile and of the number of K splits (blocks per cluster)."""
 
 from __future__ import annotations
 
@@ -13,8 +13,7 @@ SM_COUNT = 148
 EPI_BF16, EPI_F32, EPI_ACCUM, EPI_GATED = 0, 1, 2, 3
 
 _weight_maps: dict = {}
-_scratch: dict = {}           # device -> (partial, tickets); kept alive, captured graphs point here
-_retired: list = []
+MAX_SPLITS = 8                # blocks of one cluster
 
 
 def takes(x: torch.Tensor, weight: torch.Tensor) -> bool:
@@ -54,26 +53,14 @@ def token_tile(m: int, dual: bool) -> int:
 
 
 def choose_splits(n_tiles: int, m_tiles: int, k: int) -> int:
-    """Split K so that about one block per SM is busy; none when the tiles alone fill
-    most of the GPU."""
+    """Split K over a cluster so that about one block per SM is busy; no split when the
+    tiles alone fill most of the GPU."""
     tiles = n_tiles * m_tiles
     if tiles * 4 >= SM_COUNT * 3:
         return 1
     total_kb = -(-k // 64)
-    want = max(1, min(total_kb, SM_COUNT // tiles))
+    want = max(1, min(total_kb, MAX_SPLITS, SM_COUNT // tiles))
     return plain_function("sakv_gemm_tc_splits")(k, want)
-
-
-def _scratch_for(device, floats: int, tiles: int):
-    have = _scratch.get(device)
-    if have is None or have[0].numel() < floats or have[1].numel() < tiles:
-        if have is not None:
-            _retired.append(have)            # graphs captured earlier may still use it
-        partial = torch.empty(max(floats, 1 << 22), dtype=torch.float32, device=device)
-        tickets = torch.zeros(max(tiles, 4096), dtype=torch.int32, device=device)
-        have = (partial, tickets)
-        _scratch[device] = have
-    return have
 
 
 def gemm(x: torch.Tensor, weight: torch.Tensor, bias, epi: int, out: torch.Tensor,
@@ -87,14 +74,10 @@ def gemm(x: torch.Tensor, weight: torch.Tensor, bias, epi: int, out: torch.Tenso
     if splits is None:
         splits = choose_splits(n_tiles, m_tiles, k)
     splits = plain_function("sakv_gemm_tc_splits")(k, splits)
-    partial = tickets = None
-    if splits > 1:
-        floats = plain_function("sakv_gemm_tc_scratch")(mt, int(dual), n_tiles, m_tiles, splits)
-        partial, tickets = _scratch_for(x.device, floats, n_tiles * m_tiles)
     x_raw, x_map = _make_map(x, mt)
     call("sakv_gemm_tc", _weight_map(weight), x_map, m, n, k, mt, splits, epi, dual_offset,
          ptr(bias), dtype_code(bias.dtype) if bias is not None else BF16, ptr(out),
-         out.stride(0), ptr(partial), ptr(tickets))
+         out.stride(0))
     return out
 
 
