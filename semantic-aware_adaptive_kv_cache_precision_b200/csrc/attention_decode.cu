@@ -53,6 +53,17 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap k_map,
   const int group = heads / kv_heads;       // query heads per KV head (<= 16 here)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
+  let_next_kernel_start();
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      tma::mbar_init(&full[s], 1);
+      tma::mbar_init(&empty[s], kComputeWarps);
+    }
+    tma::fence_barrier_init();
+    tma::prefetch_map(&k_map);
+    tma::prefetch_map(&v_map);
+  }
+  wait_for_previous_kernel();        // lengths, block lists, queries and the newest keys
   const int kv_len = seq_lens[b];
   const int first_key = (window > 0 && kv_len - window > 0) ? kv_len - window : 0;
   const int first_tile = first_key / KT;
@@ -61,21 +72,11 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap k_map,
   const int per_split = (count + splits - 1) / splits;
   const int t0 = first_tile + split * per_split;
   const int t1 = min(n_tiles, t0 + per_split);
-
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < kStages; ++s) {
-      tma::mbar_init(&full[s], 1);
-      tma::mbar_init(&empty[s], kComputeWarps);
-    }
-    tma::fence_barrier_init();
-  }
   __syncthreads();
 
   if (warp == kComputeWarps) {
     // ---- the copy warp: one lane feeds the ring ---------------------------------
     if (lane == 0) {
-      tma::prefetch_map(&k_map);
-      tma::prefetch_map(&v_map);
       for (int t = t0, i = 0; t < t1; ++t, ++i) {
         const int stage = i % kStages;
         if (i >= kStages &&
@@ -265,6 +266,8 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap k_map,
 // out[b, h, :] = sum_s w_s o_s / sum_s w_s l_s with w_s = exp2(m_s - max m)
 __global__ void combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                __nv_bfloat16* __restrict__ out, int splits, int head_dim) {
+  let_next_kernel_start();
+  wait_for_previous_kernel();
   const long long bh = blockIdx.x;
   const float* ml = part_ml + bh * splits * 2;
   float big = -INFINITY;
@@ -301,15 +304,14 @@ int launch(const CUtensorMap* k_map, const CUtensorMap* v_map, const __nv_bfloat
     configured = true;
   }
   const dim3 grid(splits, kv_heads, sequences);
-  decode_attention_kernel<D><<<grid, kThreads, Smem<D>::kBytes, stream>>>(
-      *k_map, *v_map, q, q_stride, seq_lens, block_table, max_blocks, out, part_o, part_ml, heads,
-      kv_heads, splits, scale * 1.4426950408889634f, window, error);
-  int status = launch_status();
-  if (status == 0 && splits > 1) {
-    combine_kernel<<<sequences * heads, D <= 128 ? D : 128, 0, stream>>>(part_o, part_ml, out,
-                                                                         splits, D);
-    status = launch_status();
-  }
+  int status = launch_overlapped(decode_attention_kernel<D>, grid, dim3(kThreads), Smem<D>::kBytes,
+                                 stream, 1, *k_map, *v_map, q, q_stride, seq_lens, block_table,
+                                 max_blocks, out, part_o, part_ml, heads, kv_heads, splits,
+                                 scale * 1.4426950408889634f, window, error);
+  if (status == 0 && splits > 1)
+    status = launch_overlapped(combine_kernel, dim3(sequences * heads), dim3(D <= 128 ? D : 128),
+                               0, stream, 1, (const float*)part_o, (const float*)part_ml, out,
+                               splits, D);
   return status;
 }
 

@@ -60,6 +60,45 @@ __device__ __forceinline__ float block_sum(float v, float* scratch /* >= 33 floa
 
 static inline int launch_status() { return static_cast<int>(cudaGetLastError()); }
 
+// Programmatic dependent launch: a kernel launched with `launch_overlapped` may begin
+// (set up its shared memory, prefetch constants such as weights) while the kernel before
+// it on the stream is still running. It must call `wait_for_previous_kernel()` before it
+// reads anything that kernel wrote and before it writes global memory at all; it calls
+// `let_next_kernel_start()` at its top so that its own successor can do the same.
+__device__ __forceinline__ void wait_for_previous_kernel() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+__device__ __forceinline__ void let_next_kernel_start() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+template <typename... KernelArgs, typename... Args>
+static inline int launch_overlapped(void (*kernel)(KernelArgs...), dim3 grid, dim3 block,
+                                    size_t smem, cudaStream_t stream, int cluster_z,
+                                    Args&&... args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attr[2];
+  int n = 0;
+  attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[n].val.programmaticStreamSerializationAllowed = 1;
+  ++n;
+  if (cluster_z > 1) {
+    attr[n].id = cudaLaunchAttributeClusterDimension;
+    attr[n].val.clusterDim.x = 1;
+    attr[n].val.clusterDim.y = 1;
+    attr[n].val.clusterDim.z = cluster_z;
+    ++n;
+  }
+  config.attrs = attr;
+  config.numAttrs = n;
+  const cudaError_t e = cudaLaunchKernelEx(&config, kernel, static_cast<KernelArgs>(args)...);
+  return e != cudaSuccess ? static_cast<int>(e) : launch_status();
+}
+
 static inline int grid_for(long long work, int threads, int cap = 148 * 16) {
   long long blocks = (work + threads - 1) / threads;
   if (blocks < 1) blocks = 1;

@@ -10,6 +10,8 @@ namespace {
 template <typename Table>
 __global__ void embed_kernel(const int32_t* __restrict__ ids, const Table* __restrict__ table,
                              float* __restrict__ out, int hidden, int vocab, long long count) {
+  let_next_kernel_start();
+  wait_for_previous_kernel();
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < count;
        i += (long long)gridDim.x * blockDim.x) {
     const long long token = i / hidden;
@@ -51,13 +53,12 @@ SAKV_EXPORT int sakv_embed(const int32_t* ids, const void* table, int table_dtyp
   const long long count = (long long)tokens * hidden;
   const int grid = grid_for(count, 256);
   if (table_dtype == SAKV_F32)
-    embed_kernel<float><<<grid, 256, 0, stream>>>(ids, (const float*)table, out, hidden, vocab, count);
-  else if (table_dtype == SAKV_BF16)
-    embed_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(ids, (const __nv_bfloat16*)table, out,
-                                                          hidden, vocab, count);
-  else
-    return cudaErrorInvalidValue;
-  return launch_status();
+    return launch_overlapped(embed_kernel<float>, dim3(grid), dim3(256), 0, stream, 1, ids,
+                             (const float*)table, out, hidden, vocab, count);
+  if (table_dtype == SAKV_BF16)
+    return launch_overlapped(embed_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, stream, 1, ids,
+                             (const __nv_bfloat16*)table, out, hidden, vocab, count);
+  return cudaErrorInvalidValue;
 }
 
 SAKV_EXPORT int sakv_gated_silu(const void* gate_up, void* out, int dtype, int tokens, int inter,

@@ -148,17 +148,32 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
   __syncthreads();
   tc::fence_after_sync();
   const uint32_t tmem = *tmem_slot;
+  // Only now, with this block's shared and tensor memory in hand, may the next kernel's
+  // blocks start to arrive: they can never hold what a block of this kernel still needs.
+  let_next_kernel_start();
 
   if (warp == 0) {
     // ---- TMA producer ---------------------------------------------------------------
     if (lane == 0) {
       tma::prefetch_map(&w_map);
       tma::prefetch_map(&x_map);
-      for (int i = 0; i < n_kb; ++i) {
+      // Weights do not depend on the kernel before: the first ring of weight tiles is
+      // already on its way while that kernel finishes; the activations follow the wait.
+      const int ahead = min(n_kb, stages);
+      for (int i = 0; i < ahead; ++i) {
+        uint8_t* dst = smem + i * C::kStageBytes;
+        const int x = (kb0 + i) * BK;
+        tma::mbar_expect_tx(&full[i], C::kStageBytes);
+        tma::load_2d(dst, &w_map, x, n0, &full[i]);
+        if (kDual) tma::load_2d(dst + kWTile, &w_map, x, p.dual_offset + n0, &full[i]);
+      }
+      wait_for_previous_kernel();
+      for (int i = 0; i < ahead; ++i)
+        tma::load_2d(smem + i * C::kStageBytes + (kDual ? 2 : 1) * kWTile, &x_map,
+                     (kb0 + i) * BK, m0, &full[i]);
+      for (int i = ahead; i < n_kb; ++i) {
         const int stage = i % stages;
-        if (i >= stages &&
-            !tma::mbar_wait(&empty[stage], ((i / stages) - 1) & 1, p.error, 301))
-          break;
+        if (!tma::mbar_wait(&empty[stage], ((i / stages) - 1) & 1, p.error, 301)) break;
         uint8_t* dst = smem + stage * C::kStageBytes;
         const int x = (kb0 + i) * BK;
         tma::mbar_expect_tx(&full[stage], C::kStageBytes);
@@ -196,10 +211,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;          // lane of tensor memory = weight row in the tile
     const int n = n0 + row;
+    const float bias = bias_at(p, n);
+    wait_for_previous_kernel();       // before any write to global memory
     const bool ok = tma::mbar_wait(accum, 0, p.error, 303);
     tc::fence_after_sync();
     const uint32_t taddr = tmem + (static_cast<uint32_t>(quarter * 32) << 16);
-    const float bias = bias_at(p, n);
     if (p.splits == 1) {
       if (ok) {
 #pragma unroll 1
@@ -280,20 +296,9 @@ int launch(const CUtensorMap* w_map, const CUtensorMap* x_map, Params p, int n_t
   while (C::smem_bytes(p.stages) > 227 * 1024) --p.stages;
   if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p.error), g_error) != cudaSuccess)
     return cudaErrorInvalidValue;
-  cudaLaunchConfig_t config = {};
-  config.gridDim = dim3(n_tiles, m_tiles, p.splits);
-  config.blockDim = dim3(kThreads);
-  config.dynamicSmemBytes = C::smem_bytes(p.stages);
-  config.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = 1;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = p.splits;
-  config.attrs = attr;
-  config.numAttrs = 1;
-  const cudaError_t e = cudaLaunchKernelEx(&config, gemm_tc_kernel<MT, kDual>, *w_map, *x_map, p);
-  return e != cudaSuccess ? static_cast<int>(e) : launch_status();
+  return launch_overlapped(gemm_tc_kernel<MT, kDual>, dim3(n_tiles, m_tiles, p.splits),
+                           dim3(kThreads), (size_t)C::smem_bytes(p.stages), stream, p.splits,
+                           *w_map, *x_map, p);
 }
 
 }  // namespace

@@ -9,21 +9,62 @@
 
 namespace {
 
+// Rows up to kThreads * 4 * kPerThread wide are read once and kept in registers (the
+// weight is fetched before the reduction, so the row costs one memory round trip);
+// wider rows are read a second time.
+constexpr int kThreads = 256;
+constexpr int kPerThread = 4;          // float4 loads per thread: rows up to 4096 wide
+
 template <typename W, typename Out>
-__global__ void rmsnorm_kernel(const float* __restrict__ x, const int32_t* __restrict__ rows,
-                               const W* __restrict__ weight, Out* __restrict__ out, int hidden,
-                               float eps) {
+__global__ void __launch_bounds__(kThreads)
+rmsnorm_kernel(const float* __restrict__ x, const int32_t* __restrict__ rows,
+               const W* __restrict__ weight, Out* __restrict__ out, int hidden, float eps) {
   __shared__ float scratch[33];
+  let_next_kernel_start();
+  const bool fits = hidden <= kThreads * 4 * kPerThread && (hidden & 3) == 0;
+  float wv[kPerThread][4];
+  if (fits) {                      // the weight does not depend on the kernel before
+#pragma unroll
+    for (int i = 0; i < kPerThread; ++i) {
+      const int c = (i * kThreads + threadIdx.x) * 4;
+      if (c < hidden) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) wv[i][j] = widen(weight[c + j]);
+      }
+    }
+  }
+  wait_for_previous_kernel();
   const long long src = rows ? rows[blockIdx.x] : blockIdx.x;
   const float* in = x + src * hidden;
   Out* o = out + (long long)blockIdx.x * hidden;
+  if (fits) {
+    float4 v[kPerThread];
+    float acc = 0.f;
+#pragma unroll
+    for (int i = 0; i < kPerThread; ++i) {
+      const int c = (i * kThreads + threadIdx.x) * 4;
+      v[i] = c < hidden ? *reinterpret_cast<const float4*>(in + c) : make_float4(0, 0, 0, 0);
+      acc += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
+    }
+    const float scale = rsqrtf(block_sum(acc, scratch) / static_cast<float>(hidden) + eps);
+#pragma unroll
+    for (int i = 0; i < kPerThread; ++i) {
+      const int c = (i * kThreads + threadIdx.x) * 4;
+      if (c < hidden) {
+        o[c] = narrow<Out>(v[i].x * scale * wv[i][0]);
+        o[c + 1] = narrow<Out>(v[i].y * scale * wv[i][1]);
+        o[c + 2] = narrow<Out>(v[i].z * scale * wv[i][2]);
+        o[c + 3] = narrow<Out>(v[i].w * scale * wv[i][3]);
+      }
+    }
+    return;
+  }
   float acc = 0.f;
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
     const float v = in[i];
     acc += v * v;
   }
-  const float total = block_sum(acc, scratch);
-  const float scale = rsqrtf(total / static_cast<float>(hidden) + eps);
+  const float scale = rsqrtf(block_sum(acc, scratch) / static_cast<float>(hidden) + eps);
   for (int i = threadIdx.x; i < hidden; i += blockDim.x)
     o[i] = narrow<Out>(in[i] * scale * widen(weight[i]));
 }
@@ -35,15 +76,14 @@ SAKV_EXPORT int sakv_rmsnorm(const float* x, const int32_t* rows, const void* we
                              float eps, cudaStream_t stream) {
   if (n_rows < 0 || hidden <= 0) return cudaErrorInvalidValue;
   if (n_rows == 0) return 0;
-  const int threads = 256;
-#define LAUNCH(W, O)                                                                       \
-  rmsnorm_kernel<W, O><<<n_rows, threads, 0, stream>>>(x, rows, (const W*)weight, (O*)out, \
-                                                       hidden, eps)
+  const int threads = kThreads;
+#define LAUNCH(W, O)                                                                          \
+  return launch_overlapped(rmsnorm_kernel<W, O>, dim3(n_rows), dim3(threads), 0, stream, 1, x, \
+                           rows, (const W*)weight, (O*)out, hidden, eps)
   if (weight_dtype == SAKV_F32 && out_dtype == SAKV_F32) LAUNCH(float, float);
-  else if (weight_dtype == SAKV_F32 && out_dtype == SAKV_BF16) LAUNCH(float, __nv_bfloat16);
-  else if (weight_dtype == SAKV_BF16 && out_dtype == SAKV_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
-  else if (weight_dtype == SAKV_BF16 && out_dtype == SAKV_F32) LAUNCH(__nv_bfloat16, float);
-  else return cudaErrorInvalidValue;
+  if (weight_dtype == SAKV_F32 && out_dtype == SAKV_BF16) LAUNCH(float, __nv_bfloat16);
+  if (weight_dtype == SAKV_BF16 && out_dtype == SAKV_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
+  if (weight_dtype == SAKV_BF16 && out_dtype == SAKV_F32) LAUNCH(__nv_bfloat16, float);
 #undef LAUNCH
-  return launch_status();
+  return cudaErrorInvalidValue;
 }

@@ -26,6 +26,8 @@ __global__ void rope_store_kernel(T* __restrict__ qkv, long long row_stride,
                                   const float* __restrict__ sin_table, int rot,
                                   T* __restrict__ k_cache, T* __restrict__ v_cache, int heads,
                                   int kv_heads, int head_dim, int write_cache) {
+  let_next_kernel_start();
+  wait_for_previous_kernel();
   const int t = blockIdx.x;
   const int h = blockIdx.y;  // 0..A-1 queries, A..A+G-1 keys, A+G..A+2G-1 values
   const int pos = positions[t];
@@ -76,15 +78,14 @@ SAKV_EXPORT int sakv_rope_store(void* qkv, int dtype, long long row_stride,
   const dim3 grid(tokens, heads + 2 * kv_heads);
   const int threads = head_dim / 2 >= 64 ? 64 : 32;
   if (dtype == SAKV_F32)
-    rope_store_kernel<float><<<grid, threads, 0, stream>>>(
-        (float*)qkv, row_stride, positions, token_seq, block_table, max_blocks, cos_table,
-        sin_table, rot, (float*)k_cache, (float*)v_cache, heads, kv_heads, head_dim, write_cache);
-  else if (dtype == SAKV_BF16)
-    rope_store_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(
-        (__nv_bfloat16*)qkv, row_stride, positions, token_seq, block_table, max_blocks, cos_table,
-        sin_table, rot, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, heads, kv_heads,
-        head_dim, write_cache);
-  else
-    return cudaErrorInvalidValue;
-  return launch_status();
+    return launch_overlapped(rope_store_kernel<float>, grid, dim3(threads), 0, stream, 1,
+                             (float*)qkv, row_stride, positions, token_seq, block_table,
+                             max_blocks, cos_table, sin_table, rot, (float*)k_cache,
+                             (float*)v_cache, heads, kv_heads, head_dim, write_cache);
+  if (dtype == SAKV_BF16)
+    return launch_overlapped(rope_store_kernel<__nv_bfloat16>, grid, dim3(threads), 0, stream, 1,
+                             (__nv_bfloat16*)qkv, row_stride, positions, token_seq, block_table,
+                             max_blocks, cos_table, sin_table, rot, (__nv_bfloat16*)k_cache,
+                             (__nv_bfloat16*)v_cache, heads, kv_heads, head_dim, write_cache);
+  return cudaErrorInvalidValue;
 }

@@ -42,6 +42,8 @@ __global__ void choose_kernel(const float* __restrict__ logits, long long row_st
   __shared__ float best_s[32];
   __shared__ int at_s[32];
   __shared__ int last;
+  let_next_kernel_start();
+  wait_for_previous_kernel();
   const int r = blockIdx.y, chunks = gridDim.x;
   const float* row = logits + (long long)r * row_stride;
   unsigned long long key = 0;
@@ -118,7 +120,6 @@ SAKV_EXPORT int sakv_choose(const float* logits, long long row_stride, int rows,
   if (temperature > 0.f && (!request || !step)) return cudaErrorInvalidValue;
   if (rows == 0) return 0;
   const dim3 grid((vocab + kChunk - 1) / kChunk, rows);
-  choose_kernel<<<grid, 256, 0, stream>>>(logits, row_stride, vocab, temperature, seed, request,
-                                          step, out, chunk_best, chunk_at, tickets);
-  return launch_status();
+  return launch_overlapped(choose_kernel, grid, dim3(256), 0, stream, 1, logits, row_stride, vocab,
+                           temperature, seed, request, step, out, chunk_best, chunk_at, tickets);
 }
