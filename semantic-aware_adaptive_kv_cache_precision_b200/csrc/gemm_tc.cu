@@ -106,7 +106,9 @@ __device__ __forceinline__ void finish(const Params& p, int m, int n, float c, f
   } else if (p.epi == EPI_F32) {
     reinterpret_cast<float*>(p.out)[at] = c + bias;
   } else if (p.epi == EPI_ACCUM) {
-    reinterpret_cast<float*>(p.out)[at] += c + bias;
+    // one block adds to each element exactly once, so the sum is the same every time; the
+    // reduction instruction spares the thread the round trip of reading the old value
+    atomicAdd(reinterpret_cast<float*>(p.out) + at, c + bias);
   } else {
     const float silu = c / (1.0f + expf(-c));
     reinterpret_cast<__nv_bfloat16*>(p.out)[at] = __float2bfloat16_rn(silu * up);
@@ -248,24 +250,36 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
       const int n = n0 + row;
       const float bias = bias_at(p, n);
       const uint32_t base = tma::smem_u32(smem);
-      // token columns split, split + splits, ... are finished by this block
-      for (int c = split; c < MT && m0 + c < p.M; c += p.splits) {
-        float part[kMaxSplits], part_up[kMaxSplits];
+      // token columns split, split + splits, ... are finished by this block, four at a
+      // time so that all their partials are in flight together
+      constexpr int kBatch = 4;
+      for (int c0 = split; c0 < MT && m0 + c0 < p.M; c0 += kBatch * p.splits) {
+        float part[kBatch][kMaxSplits], part_up[kBatch][kMaxSplits];
 #pragma unroll
-        for (int s = 0; s < kMaxSplits; ++s) {
-          part[s] = part_up[s] = 0.f;
-          if (s < p.splits) {
-            part[s] = ld_peer(base + (c * BM + row) * 4, s);
-            if (kDual) part_up[s] = ld_peer(base + ((MT + c) * BM + row) * 4, s);
+        for (int j = 0; j < kBatch; ++j) {
+          const int c = c0 + j * p.splits;
+          const bool live = c < MT && m0 + c < p.M;
+#pragma unroll
+          for (int s = 0; s < kMaxSplits; ++s) {
+            part[j][s] = part_up[j][s] = 0.f;
+            if (live && s < p.splits) {
+              part[j][s] = ld_peer(base + (c * BM + row) * 4, s);
+              if (kDual) part_up[j][s] = ld_peer(base + ((MT + c) * BM + row) * 4, s);
+            }
           }
         }
-        float acc = 0.f, up = 0.f;
 #pragma unroll
-        for (int s = 0; s < kMaxSplits; ++s) {
-          acc += part[s];
-          up += part_up[s];
+        for (int j = 0; j < kBatch; ++j) {
+          const int c = c0 + j * p.splits;
+          if (c >= MT) break;
+          float acc = 0.f, up = 0.f;
+#pragma unroll
+          for (int s = 0; s < kMaxSplits; ++s) {
+            acc += part[j][s];
+            up += part_up[j][s];
+          }
+          finish(p, m0 + c, n, acc, up, bias);
         }
-        finish(p, m0 + c, n, acc, up, bias);
       }
     }
     cluster_sync_all();       // nobody leaves while a peer may still read its shared memory
@@ -354,6 +368,39 @@ SAKV_EXPORT int sakv_gemm_tc_splits(int K, int splits) {
   if (splits < 1) splits = 1;
   const int per = (total_kb + splits - 1) / splits;
   return (total_kb + per - 1) / per;
+}
+
+// How many clusters of `splits` blocks of the kernel for token tile `mt` can be resident
+// at once (0 if it cannot be asked).
+SAKV_EXPORT int sakv_gemm_tc_max_clusters(int mt, int dual, int splits) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(1, 1, splits);
+  config.blockDim = dim3(kThreads);
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = splits;
+  config.attrs = attr;
+  config.numAttrs = 1;
+  int clusters = 0;
+#define ASK(MT_, D_)                                                                           \
+  if (mt == MT_ && (dual != 0) == D_) {                                                        \
+    using C = Cfg<MT_, D_>;                                                                    \
+    const int bytes = C::smem_bytes(C::stages_for(1));                                         \
+    config.dynamicSmemBytes = bytes > 227 * 1024 ? 227 * 1024 : bytes;                         \
+    cudaFuncSetAttribute(gemm_tc_kernel<MT_, D_>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                         (int)config.dynamicSmemBytes);                                        \
+    if (cudaOccupancyMaxActiveClusters(&clusters, gemm_tc_kernel<MT_, D_>, &config) !=         \
+        cudaSuccess)                                                                           \
+      clusters = 0;                                                                            \
+    cudaGetLastError();                                                                        \
+    return clusters;                                                                           \
+  }
+  ASK(16, false) ASK(32, false) ASK(64, false) ASK(128, false) ASK(256, false)
+  ASK(16, true) ASK(32, true) ASK(64, true) ASK(128, true)
+#undef ASK
+  return 0;
 }
 
 SAKV_EXPORT int sakv_gemm_tc_error(int* value) {

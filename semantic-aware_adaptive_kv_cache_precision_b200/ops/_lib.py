@@ -45,6 +45,7 @@ PLAIN_SIGNATURES = {
     "sakv_prefill_attention_error": ("attention_prefill", [P]),
     "sakv_gemm_tc_map": ("gemm_tc", [P, P, L, L, L, I]),
     "sakv_gemm_tc_splits": ("gemm_tc", [I, I]),
+    "sakv_gemm_tc_max_clusters": ("gemm_tc", [I, I, I]),
     "sakv_gemm_tc_error": ("gemm_tc", [P]),
 }
 

@@ -52,15 +52,34 @@ def token_tile(m: int, dual: bool) -> int:
     return 128 if dual else 256
 
 
-def choose_splits(n_tiles: int, m_tiles: int, k: int) -> int:
-    """Split K over a cluster so that about one block per SM is busy; no split when the
-    tiles alone fill most of the GPU."""
+_cluster_room: dict = {}
+
+
+def _blocks_at_once(mt: int, dual: bool, splits: int) -> int:
+    """How many blocks the GPU holds at once when they come in clusters of `splits` (a
+    cluster lives inside one GPC, so large clusters leave SMs unused)."""
+    key = (mt, dual, splits)
+    if key not in _cluster_room:
+        clusters = plain_function("sakv_gemm_tc_max_clusters")(mt, int(dual), splits)
+        _cluster_room[key] = min(SM_COUNT, clusters * splits) if clusters > 0 else \
+            (SM_COUNT // splits) * splits * 3 // 4
+    return _cluster_room[key]
+
+
+def choose_splits(n_tiles: int, m_tiles: int, k: int, mt: int = 16, dual: bool = False) -> int:
+    """Split K over a cluster so that as many SMs as possible pull weights in ONE wave
+    (fewer splits on a tie); no split when the tiles alone fill most of the GPU."""
     tiles = n_tiles * m_tiles
     if tiles * 4 >= SM_COUNT * 3:
         return 1
-    total_kb = -(-k // 64)
-    want = max(1, min(total_kb, MAX_SPLITS, SM_COUNT // tiles))
-    return plain_function("sakv_gemm_tc_splits")(k, want)
+    best, best_blocks = 1, tiles
+    for splits in range(2, MAX_SPLITS + 1):
+        if plain_function("sakv_gemm_tc_splits")(k, splits) != splits:
+            continue
+        blocks = tiles * splits
+        if blocks <= _blocks_at_once(mt, dual, splits) and blocks > best_blocks:
+            best, best_blocks = splits, blocks
+    return best
 
 
 def gemm(x: torch.Tensor, weight: torch.Tensor, bias, epi: int, out: torch.Tensor,
@@ -72,7 +91,7 @@ def gemm(x: torch.Tensor, weight: torch.Tensor, bias, epi: int, out: torch.Tenso
     mt = token_tile(m, dual)
     n_tiles, m_tiles = -(-n // 128), -(-m // mt)
     if splits is None:
-        splits = choose_splits(n_tiles, m_tiles, k)
+        splits = choose_splits(n_tiles, m_tiles, k, mt, dual)
     splits = plain_function("sakv_gemm_tc_splits")(k, splits)
     x_raw, x_map = _make_map(x, mt)
     call("sakv_gemm_tc", _weight_map(weight), x_map, m, n, k, mt, splits, epi, dual_offset,
