@@ -86,6 +86,7 @@ class StepStager:
             for a in range(0, c, QUERY_TILE):
                 tiles.append((i, row + a, min(QUERY_TILE, c - a), s + a))
             row += c
+        tiles.sort(key=lambda t: -(t[3] + t[2]))     # the tiles with the most keys start first
         fields = [("token_ids", T), ("positions", T), ("token_seq", T), ("cu_seqlens", B + 1),
                   ("seq_lens", B), ("slots", B), ("want", W), ("q_tiles", 4 * len(tiles))]
         fields += [(f"table{g}", t.size) for g, t in enumerate(tables)]
