@@ -2,7 +2,9 @@
 // keys and values, split along the keys (flash-decoding) so that a small batch
 // still fills the GPU, with a second kernel that folds the splits together.
 //
-//   grid  = (splits, kv_heads, sequences); block = 4 compute warps + 1 copy warp
+//   grid  = (splits, kv_heads, sequences); block = 4 warps (registers are handed out four
+//   warps at a time, so a fifth warp for the copies would halve the occupancy; lane 0 of
+//   warp 0 issues the copies between its tiles instead)
 //   tile  = one cache block: 64 keys x head_dim, fetched by TMA (128-byte swizzle)
 //           into a ring of shared-memory stages guarded by full/empty mbarriers
 //   warp w of a block takes keys 16w..16w+15 of every tile for ALL query heads of
@@ -21,7 +23,7 @@ namespace {
 
 constexpr int KT = kCacheBlock;      // keys per tile
 constexpr int kComputeWarps = 4;
-constexpr int kThreads = (kComputeWarps + 1) * 32;
+constexpr int kThreads = kComputeWarps * 32;
 constexpr int kStages = 3;
 
 template <int D>
@@ -74,26 +76,22 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap k_map,
   const int t1 = min(n_tiles, t0 + per_split);
   __syncthreads();
 
-  if (warp == kComputeWarps) {
-    // ---- the copy warp: one lane feeds the ring ---------------------------------
-    if (lane == 0) {
-      for (int t = t0, i = 0; t < t1; ++t, ++i) {
-        const int stage = i % kStages;
-        if (i >= kStages &&
-            !tma::mbar_wait(&empty[stage], ((i / kStages) - 1) & 1, error, 101))
-          break;
-        const int block = block_table[(long long)b * max_blocks + t];
-        const int row0 = (block * kv_heads + g) * KT;
-        uint8_t* dst = smem + stage * S::kStageBytes;
-        tma::mbar_expect_tx(&full[stage], S::kStageBytes);
-        for (int x = 0; x < S::kBoxes; ++x) {
-          tma::load_2d(dst + x * (KT * 128), &k_map, x * 64, row0, &full[stage]);
-          tma::load_2d(dst + S::kTileBytes + x * (KT * 128), &v_map, x * 64, row0, &full[stage]);
-        }
-      }
+  // Tile i of this split goes to stage i % kStages. Lane 0 of warp 0 keeps the ring full:
+  // kStages tiles to begin with, then tile i + kStages once every warp has let go of tile i.
+  auto request = [&](int i) {
+    const int stage = i % kStages;
+    const int block = block_table[(long long)b * max_blocks + t0 + i];
+    const int row0 = (block * kv_heads + g) * KT;
+    uint8_t* dst = smem + stage * S::kStageBytes;
+    tma::mbar_expect_tx(&full[stage], S::kStageBytes);
+    for (int x = 0; x < S::kBoxes; ++x) {
+      tma::load_2d(dst + x * (KT * 128), &k_map, x * 64, row0, &full[stage]);
+      tma::load_2d(dst + S::kTileBytes + x * (KT * 128), &v_map, x * 64, row0, &full[stage]);
     }
-    return;
-  }
+  };
+  const int n_key_tiles = max(t1 - t0, 0);
+  if (threadIdx.x == 0)
+    for (int i = 0; i < min(kStages, n_key_tiles); ++i) request(i);
 
   // ---- compute warps ------------------------------------------------------------
   // Query rows of this warp's m16 tile: row r = head g*group + r, rows >= group are zero.
@@ -205,7 +203,15 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap k_map,
       }
     }
     __syncwarp();
-    if (lane == 0) tma::mbar_arrive(&empty[stage]);
+    if (lane == 0) {
+      tma::mbar_arrive(&empty[stage]);
+      if (warp == 0 && i + kStages < n_key_tiles) {
+        if (!tma::mbar_wait(&empty[stage], (i / kStages) & 1, error, 101)) alive = false;
+        else request(i + kStages);
+      }
+    }
+    alive = __shfl_sync(0xffffffffu, alive, 0);
+    if (!alive) break;
   }
 
   // ---- merge the four warps through shared memory ------------------------------------
@@ -297,9 +303,13 @@ int launch(const CUtensorMap* k_map, const CUtensorMap* v_map, const __nv_bfloat
   if (cudaGetSymbolAddress(reinterpret_cast<void**>(&error), g_error) != cudaSuccess)
     return cudaErrorInvalidValue;
   if (!configured) {
-    const cudaError_t e = cudaFuncSetAttribute(decode_attention_kernel<D>,
-                                               cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                               Smem<D>::kBytes);
+    cudaError_t e = cudaFuncSetAttribute(decode_attention_kernel<D>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         Smem<D>::kBytes);
+    if (e == cudaSuccess)      // all of the SM's memory as shared memory: two blocks fit
+      e = cudaFuncSetAttribute(decode_attention_kernel<D>,
+                               cudaFuncAttributePreferredSharedMemoryCarveout,
+                               cudaSharedmemCarveoutMaxShared);
     if (e != cudaSuccess) return static_cast<int>(e);
     configured = true;
   }

@@ -3,7 +3,9 @@
 // and values), for batches of sequences of unequal length and for chunks that
 // continue a cached prefix.
 //
-//   grid  = (query tiles of all sequences, heads); block = 4 compute warps + 1 copy warp
+//   grid  = (query tiles of all sequences, heads); block = 4 warps (registers are handed
+//   out four warps at a time, so a fifth warp for the copies would cost a whole block of
+//   occupancy; lane 0 of warp 0 issues the copies between its tiles instead)
 //   a query tile is up to 64 consecutive tokens of one sequence; each compute warp
 //   owns 16 of them (the rows of m16n8k16 tensor-core products) and walks over the
 //   sequence's key tiles (one cache block of 64 keys each, fetched by TMA with the
@@ -23,7 +25,7 @@ namespace {
 constexpr int KT = kCacheBlock;      // keys per tile
 constexpr int QT = 64;               // queries per tile
 constexpr int kComputeWarps = 4;
-constexpr int kThreads = (kComputeWarps + 1) * 32;
+constexpr int kThreads = kComputeWarps * 32;
 constexpr int kStages = 3;
 static_assert(QT == kComputeWarps * 16, "one m16 row tile per compute warp");
 
@@ -72,26 +74,26 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap k_map,
   }
   __syncthreads();
 
-  if (warp == kComputeWarps) {
-    if (lane == 0) {
-      tma::prefetch_map(&k_map);
-      tma::prefetch_map(&v_map);
-      for (int t = t0, i = 0; t < t1; ++t, ++i) {
-        const int stage = i % kStages;
-        if (i >= kStages &&
-            !tma::mbar_wait(&empty[stage], ((i / kStages) - 1) & 1, error, 201))
-          break;
-        const int block = block_table[(long long)b * max_blocks + t];
-        const int krow0 = (block * kv_heads + g) * KT;
-        uint8_t* dst = smem + stage * S::kStageBytes;
-        tma::mbar_expect_tx(&full[stage], S::kStageBytes);
-        for (int x = 0; x < S::kBoxes; ++x) {
-          tma::load_2d(dst + x * (KT * 128), &k_map, x * 64, krow0, &full[stage]);
-          tma::load_2d(dst + S::kTileBytes + x * (KT * 128), &v_map, x * 64, krow0, &full[stage]);
-        }
-      }
+  // Tile i of the sequence's keys goes to stage i % kStages. Lane 0 of warp 0 keeps the
+  // ring full: it starts with kStages tiles and, after its own tile i, asks for tile
+  // i + kStages as soon as every warp has let go of tile i.
+  auto request = [&](int i) {
+    const int t = t0 + i;
+    const int stage = i % kStages;
+    const int block = block_table[(long long)b * max_blocks + t];
+    const int krow0 = (block * kv_heads + g) * KT;
+    uint8_t* dst = smem + stage * S::kStageBytes;
+    tma::mbar_expect_tx(&full[stage], S::kStageBytes);
+    for (int x = 0; x < S::kBoxes; ++x) {
+      tma::load_2d(dst + x * (KT * 128), &k_map, x * 64, krow0, &full[stage]);
+      tma::load_2d(dst + S::kTileBytes + x * (KT * 128), &v_map, x * 64, krow0, &full[stage]);
     }
-    return;
+  };
+  const int n_key_tiles = t1 - t0;
+  if (threadIdx.x == 0) {
+    tma::prefetch_map(&k_map);
+    tma::prefetch_map(&v_map);
+    for (int i = 0; i < min(kStages, n_key_tiles); ++i) request(i);
   }
 
   // ---- compute warps: rows warp*16 + lane/4 and + 8 of the query tile -----------------
@@ -220,7 +222,15 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap k_map,
       }
     }
     __syncwarp();
-    if (lane == 0) tma::mbar_arrive(&empty[stage]);
+    if (lane == 0) {
+      tma::mbar_arrive(&empty[stage]);
+      if (warp == 0 && i + kStages < n_key_tiles) {
+        if (!tma::mbar_wait(&empty[stage], (i / kStages) & 1, error, 201)) alive = false;
+        else request(i + kStages);
+      }
+    }
+    alive = __shfl_sync(0xffffffffu, alive, 0);
+    if (!alive) break;
   }
   if (!alive) return;
 
@@ -254,9 +264,13 @@ int launch(const CUtensorMap* k_map, const CUtensorMap* v_map, const __nv_bfloat
   if (cudaGetSymbolAddress(reinterpret_cast<void**>(&error), g_error) != cudaSuccess)
     return cudaErrorInvalidValue;
   if (!configured) {
-    const cudaError_t e = cudaFuncSetAttribute(prefill_attention_kernel<D>,
-                                               cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                               Smem<D>::kBytes);
+    cudaError_t e = cudaFuncSetAttribute(prefill_attention_kernel<D>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         Smem<D>::kBytes);
+    if (e == cudaSuccess)      // all of the SM's memory as shared memory: two blocks fit
+      e = cudaFuncSetAttribute(prefill_attention_kernel<D>,
+                               cudaFuncAttributePreferredSharedMemoryCarveout,
+                               cudaSharedmemCarveoutMaxShared);
     if (e != cudaSuccess) return static_cast<int>(e);
     configured = true;
   }
