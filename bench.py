@@ -243,8 +243,75 @@ def reference_arm(args) -> int:
     return 0
 
 
+def kernel_case(name: str) -> int:
+    """Run ONE kernel of the decode or prefill step a few times on inputs of the benchmark's
+    sizes, for a profiler to capture (`ncu -k regex:... -c 1 python bench.py --kernel NAME`).
+    Nothing is timed or printed beyond a line that says what ran."""
+    import torch
+    from semantic_aware_adaptive_kv_cache_precision_b200 import ops
+    from semantic_aware_adaptive_kv_cache_precision_b200.ops import gemm_tc
+    c = QWEN25_1P5B
+    H, A, G, I, V = (c["hidden_size"], c["num_attention_heads"], c["num_key_value_heads"],
+                     c["intermediate_size"], c["vocab_size"])
+    d = H // A
+    torch.manual_seed(0)
+    dev = "cuda"
+
+    def weights(n, k, copies):
+        return [torch.randn(n, k, device=dev, dtype=torch.bfloat16) * 0.02 for _ in range(copies)]
+
+    if name.startswith("gemm_"):
+        _, which, batch = name.split("_", 2)
+        m = int(batch.lstrip("b"))
+        if which == "gateup":
+            ws, x = weights(2 * I, H, 3), torch.randn(m, H, device=dev, dtype=torch.bfloat16)
+            out = torch.empty(m, I, device=dev, dtype=torch.bfloat16)
+            run = lambda i: gemm_tc.gemm(x, ws[i % 3], None, gemm_tc.EPI_GATED, out, I, dual_offset=I)
+        elif which == "down":
+            ws, x = weights(H, I, 3), torch.randn(m, I, device=dev, dtype=torch.bfloat16)
+            out = torch.zeros(m, H, device=dev, dtype=torch.float32)
+            run = lambda i: gemm_tc.gemm(x, ws[i % 3], None, gemm_tc.EPI_ACCUM, out, H)
+        elif which == "head":
+            ws, x = weights(V, H, 1), torch.randn(m, H, device=dev, dtype=torch.bfloat16)
+            out = torch.empty(m, V, device=dev, dtype=torch.float32)
+            run = lambda i: gemm_tc.gemm(x, ws[0], None, gemm_tc.EPI_F32, out, V)
+        else:
+            raise SystemExit(f"unknown kernel case {name}")
+    elif name.startswith("attention_decode_"):
+        batch = int(name.rsplit("_", 1)[1].lstrip("b"))
+        blocks_per = CONTEXT // 64 + 1
+        k = torch.randn(batch * blocks_per, G, 64, d, device=dev, dtype=torch.bfloat16)
+        v = torch.randn_like(k)
+        table = torch.arange(batch * blocks_per, dtype=torch.int32, device=dev).view(batch, blocks_per)
+        table = torch.nn.functional.pad(table, (0, 40 - blocks_per), value=-1).contiguous()
+        lens = torch.full((batch,), CONTEXT + 5, dtype=torch.int32, device=dev)
+        qkv = torch.randn(batch, (A + 2 * G) * d, device=dev, dtype=torch.bfloat16)
+        run = lambda i: ops.attention_decode(qkv, k, v, lens, table, A, G, d, d ** -0.5, None,
+                                             CONTEXT + 5)
+    elif name == "attention_prefill_2048":
+        n = PREFILL_TOKENS
+        k = torch.randn(n // 64, G, 64, d, device=dev, dtype=torch.bfloat16)
+        v = torch.randn_like(k)
+        table = torch.arange(n // 64, dtype=torch.int32, device=dev).view(1, -1).contiguous()
+        tiles = torch.tensor([(0, s, 64, s) for s in range(n - 64, -1, -64)], dtype=torch.int32,
+                             device=dev)
+        lens = torch.tensor([n], dtype=torch.int32, device=dev)
+        qkv = torch.randn(n, (A + 2 * G) * d, device=dev, dtype=torch.bfloat16)
+        run = lambda i: ops.attention_prefill(qkv, k, v, tiles, lens, table, A, G, d, d ** -0.5, None)
+    else:
+        raise SystemExit(f"unknown kernel case {name}")
+    for i in range(4):
+        run(i)
+    torch.cuda.synchronize()
+    print(f"ran {name} 4 times")
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
+    ap.add_argument("--kernel", default=None,
+                    help="run one kernel case for a profiler: gemm_gateup_b8, gemm_down_b8, "
+                         "gemm_head_b8, attention_decode_b64, attention_prefill_2048")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=3)
@@ -259,6 +326,8 @@ def main() -> int:
     if args.gpus != 1:
         print(f"bench.py: this library runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
+    if args.kernel:
+        return kernel_case(args.kernel)
     if args.warmup < 3:
         args.warmup = 3
     if args.impl == "reference":

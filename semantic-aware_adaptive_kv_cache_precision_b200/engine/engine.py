@@ -17,6 +17,7 @@ import numpy as np
 import torch
 
 from .. import sampling
+from ..ops import _lib
 from ..cache import BLOCK, CacheFull, SequenceCache
 from ..config import config_from_dict, config_from_folder
 from .generate import (COMPLETE, DECODING, EXHAUSTED, PREFILLING, Ending, RequestState,
@@ -188,11 +189,14 @@ class Engine:
             if self._graph_pool is None:
                 self._graph_pool = torch.cuda.graph_pool_handle()
             torch.cuda.synchronize(self.device)
+            before = _lib.launches
             with torch.cuda.graph(graph, pool=self._graph_pool):
                 out = self.model.logits(self.model.hidden(ctx, cache), ctx.want)
-            entry = (graph, out)
+            entry = (graph, out, _lib.launches - before)
             self._graphs[key] = entry
+            _lib.launches = before
         entry[0].replay()
+        _lib.launches += entry[2]            # the kernels of this library inside the graph
         return entry[1].clone()
 
     # -- whole sequences ---------------------------------------------------------------

@@ -242,3 +242,32 @@ def test_cache_full_ends_requests_gracefully(model_folders):
     assert engine.cache.lengths[slot] == 64
     engine.close([slot])
     engine.cache.check()
+
+
+@pytest.mark.parametrize("name", ["C", "D"])
+def test_graph_replayed_decode_equals_eager_decode(name, model_folders):
+    """Decode steps are captured in a CUDA graph per batch shape and replayed; the logits
+    must be those of the same steps run kernel by kernel. The sequences cross a block
+    boundary and a change of the block lists' width on the way, and one ends early."""
+    folder = model_folders(name, "bfloat16")
+    prompts = prompts_for(name, [60, 500, 129], seed=40)
+    runs = {}
+    for graphs in (True, False):
+        engine = engine_for(folder, "bfloat16", cuda_graphs=graphs)
+        slots = engine.open(3)
+        engine.step(slots, [p[:-30] for p in prompts])
+        rows = []
+        live = [0, 1, 2]
+        for t in range(30):
+            if t == 12:
+                engine.close([slots[2]])
+                live = [0, 1]
+            out = engine.step([slots[i] for i in live],
+                              [prompts[i][len(prompts[i]) - 30 + t:len(prompts[i]) - 29 + t]
+                               for i in live])
+            rows.append(out.cpu().numpy())
+        engine.close([slots[i] for i in live])
+        runs[graphs] = np.concatenate(rows)
+        if graphs:
+            assert len(engine._graphs) >= 2          # two batch sizes were captured
+    np.testing.assert_array_equal(runs[True], runs[False])
