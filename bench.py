@@ -321,6 +321,8 @@ def main() -> int:
                     help="fewer layers than the configuration has (recorded in config)")
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 and 64")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-check", action="store_true",
+                    help="skip the comparison of the bf16 logits with the fp32 path's")
     args = ap.parse_args()
 
     if args.gpus != 1:
@@ -442,6 +444,37 @@ def main() -> int:
                "h2d_bytes_per_step": engine._stager.last_bytes,
                "d2h_bytes_per_step": 4 * args.batch, "ms_per_step": round(step_s * 1e3, 4)}
 
+    # -- the fp32 check pass: same weights, everything in true 32-bit -------------------------
+    check = None
+    if not args.no_check:
+        ids = [rng.integers(0, cfg.vocab_size, n) for n in (128, 37, 64, 1)]
+        tails = [rng.integers(0, cfg.vocab_size, 8) for _ in ids]
+
+        def logits_of(eng):
+            slots = eng.open(len(ids))
+            rows = [eng.step(slots, ids).float().cpu().numpy()]
+            for t in range(8):
+                rows.append(eng.step(slots, [tail[t:t + 1] for tail in tails]).cpu().numpy())
+            eng.close(slots)
+            return np.concatenate(rows)
+
+        got = logits_of(engine)
+        del engine
+        torch.cuda.empty_cache()
+        exact = sakv.Engine(config=cfg, dtype="float32", random_seed=0, max_batch=4,
+                            max_tokens=4 * 256).load_weights()
+        want = logits_of(exact)
+        del exact
+        p = np.exp(want - want.max(-1, keepdims=True))
+        p /= p.sum(-1, keepdims=True)
+        logq = got - got.max(-1, keepdims=True)
+        logq -= np.log(np.exp(logq).sum(-1, keepdims=True))
+        kl = float((p * (np.log(p + 1e-30) - logq)).sum(-1).mean())
+        check = {"positions": int(want.shape[0]),
+                 "top1_agreement": round(float((got.argmax(-1) == want.argmax(-1)).mean()), 4),
+                 "mean_kl": float(f"{kl:.3e}"),
+                 "max_abs_logit_diff": round(float(np.abs(got - want).max()), 4)}
+
     line = {
         "metric": "decode tokens/s (Qwen2.5-1.5B shape, batch 8, 2048 cached tokens)",
         "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W,
@@ -465,6 +498,8 @@ def main() -> int:
     }
     if e2e is not None:
         line["e2e"] = e2e
+    if check is not None:
+        line["fp32_check"] = check
     print(json.dumps(line))
     return 0
 

@@ -271,3 +271,35 @@ def test_graph_replayed_decode_equals_eager_decode(name, model_folders):
         if graphs:
             assert len(engine._graphs) >= 2          # two batch sizes were captured
     np.testing.assert_array_equal(runs[True], runs[False])
+
+
+@pytest.mark.parametrize("stored", ["float32", "float16"])
+def test_bfloat16_mode_on_checkpoints_stored_in_other_types(stored, model_folders, tmp_path):
+    """With dtype bfloat16, a tensor stored in 32 bits stays in 32 bits on the device (its
+    products then run in true fp32), and float16 is kept as bfloat16. Either way the logits
+    agree with the plain model within the bf16 bound."""
+    import json
+    import torch
+    from semantic_aware_adaptive_kv_cache_precision_b200.weights import (SafetensorsFile,
+                                                                          write_safetensors)
+    src = model_folders("C", "float32")
+    folder = tmp_path / f"c_{stored}"
+    folder.mkdir()
+    config = json.loads((src / "config.json").read_text())
+    config["torch_dtype"] = stored
+    (folder / "config.json").write_text(json.dumps(config))
+    f = SafetensorsFile(src / "model.safetensors")
+    dtype = {"float32": torch.float32, "float16": torch.float16}[stored]
+    write_safetensors(folder / "model.safetensors", {n: f.tensor(n).to(dtype) for n in f.infos})
+    engine = engine_for(folder, "bfloat16")
+    held = {t.dtype for t in (engine.model.embed, engine.model.blocks[0].mixer.w_qkv,
+                              engine.model.blocks[0].mixer_norm.weight)}
+    assert held == ({torch.float32} if stored == "float32" else {torch.bfloat16})
+    for ids in prompts_for("C", [70, 200], seed=50):
+        whole = engine.forward(ids)
+        assert_close_to_plain(whole, plain_logits(folder, ids), "bfloat16", f"stored {stored}")
+        (slot,) = engine.open(1)
+        rows = [engine.step([slot], [ids[:-5]], [list(range(len(ids) - 5))]).cpu().numpy()]
+        rows += [engine.step([slot], [ids[t:t + 1]]).cpu().numpy() for t in range(len(ids) - 5, len(ids))]
+        engine.close([slot])
+        assert_same_logits(np.concatenate(rows), whole, "bfloat16", f"stored {stored}, stepped")

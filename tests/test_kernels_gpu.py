@@ -526,3 +526,20 @@ def test_gemm_tc_refuses_what_it_cannot_take():
     out = ops.linear(x, w)                                            # the library product runs
     assert out.shape == (4, 128)
     assert not gemm_tc.takes(x.float(), w)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_vector_paths_of_the_elementwise_kernels(dtype):
+    """Widths that are multiples of 8 take the 16-byte paths; they must agree with the
+    scalar paths (odd widths) on the same values."""
+    rng = np.random.default_rng(12)
+    gate = rng.standard_normal((33, 176)) * 3
+    up = rng.standard_normal((33, 176))
+    wide = ops.gated_silu(dev(np.concatenate([gate, up], axis=1), dtype))
+    narrow = ops.gated_silu(dev(np.concatenate([gate[:, :175], up[:, :175]], axis=1), dtype))
+    assert torch.equal(wide[:, :175], narrow)
+    acc = dev(rng.standard_normal((7, 64)))
+    y = dev(rng.standard_normal((7, 64)), dtype)
+    want = host(acc) + host(y)
+    ops.add_into(acc, y)
+    np.testing.assert_allclose(host(acc), want, rtol=0, atol=1e-6)
