@@ -452,7 +452,7 @@ def main() -> int:
 
         def logits_of(eng):
             slots = eng.open(len(ids))
-            rows = [eng.step(slots, ids).float().cpu().numpy()]
+            rows = [eng.step(slots, ids, [list(range(len(i))) for i in ids]).float().cpu().numpy()]
             for t in range(8):
                 rows.append(eng.step(slots, [tail[t:t + 1] for tail in tails]).cpu().numpy())
             eng.close(slots)
