@@ -18,8 +18,11 @@ import torch
 from . import gemm_tc
 from ._lib import KernelError, call, ptr, require_cuda
 
-#: up to this many tokens the library's own tcgen05 kernel runs; above it, cuBLAS
-TC_MAX_TOKENS = 256
+#: up to this many tokens the library's own tcgen05 kernel runs (weights on the MMA's rows:
+#: made for decode); above it cuBLAS, whose 2-CTA kernels win once the tensor cores matter
+#: (measured at 128 tokens: 4.5 / 14.8 / 88 us against 8.6 / 27.9 / 137 us for QKV, gate-up
+#: and the LM head)
+TC_MAX_TOKENS = 64
 
 
 def gated_up(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
