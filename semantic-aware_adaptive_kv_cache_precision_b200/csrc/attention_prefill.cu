@@ -157,7 +157,8 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap k_map,
         }
       }
     }
-    // scale and mask; a tile wholly inside every row's view needs no mask
+    // Mask (a tile wholly inside every row's view needs none), then the running maximum
+    // of the raw scores; the scale is applied inside the exponent: p = 2^(s * c - m).
     const bool needs_mask = key0 + KT - 1 > pos0 || (window > 0 && key0 < last_pos - window + 1);
     float tile_max[2] = {-INFINITY, -INFINITY};
 #pragma unroll
@@ -165,22 +166,21 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap k_map,
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int r = e >> 1;
-        float v = s[nt][e] * scale_log2e;
         if (needs_mask) {
           const int key = key0 + nt * 8 + (lane & 3) * 2 + (e & 1);
           const bool seen = key <= p_row[r] && (window <= 0 || key > p_row[r] - window);
-          v = seen ? v : -INFINITY;
+          s[nt][e] = seen ? s[nt][e] : -INFINITY;
         }
-        s[nt][e] = v;
-        tile_max[r] = fmaxf(tile_max[r], v);
+        tile_max[r] = fmaxf(tile_max[r], s[nt][e]);
       }
-    float corr[2];
+    float corr[2], m_use[2];
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
       tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 1));
       tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 2));
-      const float m_new = fmaxf(m[r], tile_max[r]);
-      corr[r] = (m_new == -INFINITY) ? 1.f : exp2f(m[r] - m_new);
+      const float m_new = fmaxf(m[r], tile_max[r] * scale_log2e);
+      m_use[r] = (m_new == -INFINITY) ? 0.f : m_new;      // a row that has seen nothing yet
+      corr[r] = mma::exp2_fast(m[r] - m_use[r]);
       m[r] = m_new;
       l[r] *= corr[r];
     }
@@ -189,14 +189,16 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap k_map,
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int r = e >> 1;
-        const float p = (m[r] == -INFINITY) ? 0.f : exp2f(s[nt][e] - m[r]);
+        const float p = mma::exp2_fast(fmaf(s[nt][e], scale_log2e, -m_use[r]));
         s[nt][e] = p;
         l[r] += p;
       }
+    if (__any_sync(0xffffffffu, corr[0] != 1.f || corr[1] != 1.f)) {
 #pragma unroll
-    for (int nt = 0; nt < D / 8; ++nt) {
-      o[nt][0] *= corr[0]; o[nt][1] *= corr[0];
-      o[nt][2] *= corr[1]; o[nt][3] *= corr[1];
+      for (int nt = 0; nt < D / 8; ++nt) {
+        o[nt][0] *= corr[0]; o[nt][1] *= corr[0];
+        o[nt][2] *= corr[1]; o[nt][3] *= corr[1];
+      }
     }
     // O += P V: four k-steps of 16 keys
     {
