@@ -164,7 +164,8 @@ class Engine:
         with torch.cuda.device(self.device):
             cache.reserve(slots, ends)
             ctx = self._stager.build(slots, new_tokens, starts, rows, cache.tables_for(slots))
-            if self.cuda_graphs and ctx.is_decode and rows == list(range(len(slots))):
+            if self.cuda_graphs and self.model.graph_safe and ctx.is_decode \
+                    and rows == list(range(len(slots))):
                 logits = self._decode_by_graph(ctx, cache)
             else:
                 x = self.model.hidden(ctx, cache)
@@ -190,8 +191,21 @@ class Engine:
                 self._graph_pool = torch.cuda.graph_pool_handle()
             torch.cuda.synchronize(self.device)
             before = _lib.launches
-            with torch.cuda.graph(graph, pool=self._graph_pool):
-                out = self.model.logits(self.model.hidden(ctx, cache), ctx.want)
+            try:
+                with torch.cuda.graph(graph, pool=self._graph_pool):
+                    out = self.model.logits(self.model.hidden(ctx, cache), ctx.want)
+            except Exception:
+                # A part of this model does something a graph cannot hold (it reads a value
+                # back on the host, say, to route tokens). Nothing ran during the failed
+                # capture; from now on this engine runs its decode steps kernel by kernel.
+                self.cuda_graphs = False
+                self._graphs.clear()
+                _lib.launches = before
+                try:
+                    torch.cuda.synchronize(self.device)
+                except Exception:
+                    pass
+                return self.model.logits(self.model.hidden(ctx, cache), ctx.want)
             entry = (graph, out, _lib.launches - before)
             self._graphs[key] = entry
             _lib.launches = before

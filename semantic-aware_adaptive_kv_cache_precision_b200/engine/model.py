@@ -31,6 +31,8 @@ class DecoderModel:
             raise ValueError("cache entries of the run order must be numbered 0, 1, 2, ...")
         self._owners = owners
         self.arena = None
+        #: whether every part says its step can be captured in a CUDA graph
+        self.graph_safe = all(getattr(b, "graph_safe", True) for b in self.blocks)
 
     # -- tensors ----------------------------------------------------------------
 

@@ -49,7 +49,7 @@ class GQAAttention(Part):
         decls.append(TensorDecl(f"{p}o_proj.weight", (s.hidden, q)))
         if s.out_bias:
             decls.append(TensorDecl(f"{p}o_proj.bias", (s.hidden,)))
-        return decls
+        return decls + self.position.tensor_decls()       # a learned position table, if any
 
     def bind(self, arena):
         p = self.prefix
@@ -64,6 +64,7 @@ class GQAAttention(Part):
                 self.b_qkv = torch.cat([arena.view(f"{p}{n}.bias") for n in names])
         self.w_o = arena.view(p + "o_proj.weight")
         self.b_o = arena.view(p + "o_proj.bias") if self.spec.out_bias else None
+        self.position.bind(arena)
 
     def prepare(self, device, max_positions):
         self.position.prepare(device, max_positions)

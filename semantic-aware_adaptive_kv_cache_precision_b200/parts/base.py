@@ -48,6 +48,11 @@ class Part:
     """Base of all parts. `mode` is 'bfloat16' or 'float32': the type of
     activations between kernels (the residual stream is fp32 in both)."""
 
+    #: False for a part whose step cannot be captured in a CUDA graph (it synchronises with
+    #: the host, or launches work whose shape depends on the data). The engine then runs
+    #: decode steps kernel by kernel; it also falls back by itself if a capture fails.
+    graph_safe = True
+
     def __init__(self, spec, prefix: str, mode: str):
         self.spec, self.prefix, self.mode = spec, prefix, mode
         self.act_dtype = torch.float32 if mode == "float32" else torch.bfloat16

@@ -16,6 +16,7 @@ class PreNormBlock(Part):
         self.ffn_norm = build_part(spec.ffn_norm, p + spec.ffn_norm_name, mode)
         self.ffn = build_part(spec.ffn, p + spec.ffn_name + ".", mode)
         self.parts = (self.mixer_norm, self.mixer, self.ffn_norm, self.ffn)
+        self.graph_safe = all(getattr(part, "graph_safe", True) for part in self.parts)
 
     def tensor_decls(self):
         return [d for part in self.parts for d in part.tensor_decls()]

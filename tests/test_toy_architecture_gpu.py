@@ -201,3 +201,187 @@ def test_toy_architecture_registers_builds_and_steps(dtype, tmp_path):
     engine.cache.check()
     out = engine.generate([p.tolist() for p in prompts[:2]], 5, stop_at_eos=False)
     assert [len(o) for o in out] == [5, 5]
+
+
+# ---- a second toy: a routed feed-forward and another position encoding -----------------------
+# Attention with a learned table of position vectors added to queries and keys (instead of a
+# rotation), and a feed-forward of small experts with top-2 routing. Both are defined here,
+# registered from here, and use the package only through its part interfaces.
+
+@dataclass(frozen=True)
+class AddedPositionSpec:
+    head_dim: int
+    max_positions: int
+    kind: str = "toy_added_position"
+
+
+class AddedPosition(Part):
+    """q += P[pos], k += P[pos] with a learned table P [positions, head_dim]."""
+
+    def tensor_decls(self):
+        return [TensorDecl(self.prefix + "position_table", (self.spec.max_positions,
+                                                            self.spec.head_dim))]
+
+    def bind(self, arena):
+        self.table = arena.view(self.prefix + "position_table")
+
+    def rotate_store(self, qkv, step, view, heads, kv_heads, head_dim, write_cache=True):
+        from semantic_aware_adaptive_kv_cache_precision_b200 import ops
+        rows = self.table[step.positions.long()].to(qkv.dtype)             # [T, d]
+        qk = qkv[:, :(heads + kv_heads) * head_dim].view(qkv.shape[0], heads + kv_heads, head_dim)
+        qk += rows[:, None, :]
+        ops.rope_store(qkv, step.positions, step.token_seq, view.block_table, None, None,
+                       view.keys, view.values, heads, kv_heads, head_dim, write_cache)
+
+
+register_part("toy_added_position", AddedPosition)
+
+
+@dataclass(frozen=True)
+class RoutedSpec:
+    hidden: int
+    inner: int
+    experts: int
+    top: int
+    kind: str = "toy_routed_ffn"
+
+
+class RoutedFFN(Part):
+    """residual += sum over the top experts e of p_e * W2_e silu(W1_e h); the router's
+    logits and softmax are fp32."""
+
+    def tensor_decls(self):
+        s, p = self.spec, self.prefix
+        decls = [TensorDecl(p + "router.weight", (s.experts, s.hidden))]
+        for e in range(s.experts):
+            decls += [TensorDecl(f"{p}experts.{e}.w1", (s.inner, s.hidden)),
+                      TensorDecl(f"{p}experts.{e}.w2", (s.hidden, s.inner))]
+        return decls
+
+    def bind(self, arena):
+        p = self.prefix
+        self.router = arena.view(p + "router.weight")
+        self.w1 = [arena.view(f"{p}experts.{e}.w1") for e in range(self.spec.experts)]
+        self.w2 = [arena.view(f"{p}experts.{e}.w2") for e in range(self.spec.experts)]
+
+    def forward(self, h, step, residual):
+        from semantic_aware_adaptive_kv_cache_precision_b200 import ops
+        logits = h.float() @ self.router.float().t()
+        top_v, top_i = logits.topk(self.spec.top, dim=-1)
+        weight = torch.softmax(top_v, dim=-1)
+        for e in range(self.spec.experts):
+            rows, which = (top_i == e).nonzero(as_tuple=True)
+            if rows.numel() == 0:
+                continue
+            x = h[rows].contiguous()
+            inner = ops.linear(x, self.w1[e], out_dtype=torch.float32)
+            act = (inner / (1 + torch.exp(-inner))).to(h.dtype)
+            y = ops.linear(act, self.w2[e], out_dtype=torch.float32)
+            residual.index_add_(0, rows, y * weight[rows, which][:, None])
+
+
+register_part("toy_routed_ffn", RoutedFFN)
+
+
+@dataclass(frozen=True)
+class RoutedConfig:
+    hidden_size: int = 64
+    num_attention_heads: int = 4
+    num_key_value_heads: int = 2
+    inner_size: int = 40
+    num_experts: int = 5
+    top_k: int = 2
+    dense_size: int = 96
+    vocab_size: int = 150
+    rms_norm_eps: float = 1e-6
+    max_position_embeddings: int = 320
+
+    @classmethod
+    def from_dict(cls, raw):
+        return cls(**{k: raw[k] for k in cls.__dataclass_fields__ if k in raw})
+
+    def to_dict(self):
+        return {**self.__dict__, "architectures": ["ToyRoutedForTests"]}
+
+    def model_spec(self):
+        h, d = self.hidden_size, self.hidden_size // self.num_attention_heads
+        norm = NormSpec(h, self.rms_norm_eps)
+        attn = AttentionSpec(hidden=h, heads=self.num_attention_heads,
+                             kv_heads=self.num_key_value_heads, head_dim=d, qkv_bias=False,
+                             out_bias=True, scale=d ** -0.5, window=None,
+                             position=AddedPositionSpec(d, self.max_position_embeddings))
+        routed = RoutedSpec(h, self.inner_size, self.num_experts, self.top_k)
+        dense = GatedMLPSpec(h, self.dense_size, "silu")
+        # layer 0: routed feed-forward, layer 1: dense, layer 2: routed
+        blocks = tuple(BlockSpec(f"model.layers.{i}.", attn, norm, ffn, norm)
+                       for i, ffn in enumerate((routed, dense, routed)))
+        return ModelSpec(architecture="ToyRoutedForTests", vocab_size=self.vocab_size, hidden=h,
+                         blocks=blocks, run_order=tuple(LayerCall(i, i) for i in range(3)),
+                         final_norm=norm, tie_head=False,
+                         max_positions=self.max_position_embeddings, stored_dtype="float32")
+
+
+sakv.register_architecture("ToyRoutedForTests", RoutedConfig)
+
+
+def plain_routed(config: RoutedConfig, t: dict, ids) -> np.ndarray:
+    n = len(ids)
+    heads, kvh = config.num_attention_heads, config.num_key_value_heads
+    d = config.hidden_size // heads
+    eps = config.rms_norm_eps
+    x = plain.embed(t["model.embed_tokens.weight"], ids)
+    for i in range(3):
+        p = f"model.layers.{i}."
+        a = p + "self_attn."
+        h = plain.rms_norm(x, t[p + "input_layernorm.weight"], eps)
+        table = t[a + "position_table"][:n]
+        q = plain.linear(h, t[a + "q_proj.weight"]).reshape(n, heads, d) + table[:, None, :]
+        k = plain.linear(h, t[a + "k_proj.weight"]).reshape(n, kvh, d) + table[:, None, :]
+        v = plain.linear(h, t[a + "v_proj.weight"]).reshape(n, kvh, d)
+        out = np.empty((n, heads, d))
+        for hd in range(heads):
+            g = hd // (heads // kvh)
+            s = np.where(plain.causal_mask(n), q[:, hd] @ k[:, g].T / np.sqrt(d), -np.inf)
+            out[:, hd] = plain.softmax(s) @ v[:, g]
+        x = x + plain.linear(out.reshape(n, -1), t[a + "o_proj.weight"], t[a + "o_proj.bias"])
+        h = plain.rms_norm(x, t[p + "post_attention_layernorm.weight"], eps)
+        if i == 1:
+            w = {k_[len(p + "mlp."):]: v_ for k_, v_ in t.items() if k_.startswith(p + "mlp.")}
+            x = x + plain.swiglu_mlp(h, w)
+            continue
+        logits = h @ t[p + "mlp.router.weight"].T
+        y = np.zeros_like(x)
+        for row in range(n):
+            top = np.argsort(-logits[row], kind="stable")[:config.top_k]
+            pw = plain.softmax(logits[row, top][None, :])[0]
+            for e, pe in zip(top, pw):
+                inner = h[row] @ t[f"{p}mlp.experts.{e}.w1"].T
+                y[row] += pe * ((inner / (1 + np.exp(-inner))) @ t[f"{p}mlp.experts.{e}.w2"].T)
+        x = x + y
+    return plain.rms_norm(x, t["model.norm.weight"], eps) @ t["lm_head.weight"].T
+
+
+def test_routed_feed_forward_and_another_position_encoding(tmp_path):
+    config = RoutedConfig()
+    folder = sakv.write_random_model(tmp_path / "routed", config, seed=7)
+    engine = sakv.Engine(folder, dtype="float32", max_tokens=1024).load_weights()
+    _, tensors = plain.read_model_folder(folder)
+    # make the routing matter: spread the router's logits
+    rng = np.random.default_rng(1)
+    prompts = [rng.integers(0, config.vocab_size, n) for n in (40, 5, 90)]
+    want = [plain_routed(config, tensors, p) for p in prompts]
+    for p, w in zip(prompts, want):
+        got = engine.forward(p)
+        assert np.abs(got - w).max() <= 5e-5 * np.abs(w).max()
+    slots = engine.open(3)
+    heads = [len(p) - 3 for p in prompts]
+    out = engine.step(slots, [p[:h] for p, h in zip(prompts, heads)],
+                      [list(range(h)) for h in heads]).cpu().numpy()
+    rows = [[out[sum(heads[:i]):sum(heads[:i + 1])]] for i in range(3)]
+    for t_ in range(3):
+        step_out = engine.step(slots, [p[h + t_:h + t_ + 1] for p, h in zip(prompts, heads)])
+        for i in range(3):
+            rows[i].append(step_out[i:i + 1].cpu().numpy())
+    engine.close(slots)
+    for i in range(3):
+        assert np.abs(np.concatenate(rows[i]) - want[i]).max() <= 5e-5 * np.abs(want[i]).max()
