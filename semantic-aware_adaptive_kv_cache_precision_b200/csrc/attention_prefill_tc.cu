@@ -1,0 +1,347 @@
+// Prefill attention on tcgen05 tensor cores, head size 128: causal grouped-query flash
+// attention of the step's new tokens over their sequences' caches, for batches of unequal
+// lengths and for chunks that continue a cached prefix (the same contract as the mma.sync
+// kernel in attention_prefill.cu, which serves head size 64 and is this kernel's test twin).
+//
+//   grid  = (query tiles of up to 128 tokens, heads); block = 6 warps:
+//     warp 0     TMA: the query tile once, then the sequence's key/value blocks (64 keys, one
+//                cache block each) into a ring of stages,
+//     warp 1     one lane issues every tcgen05.mma and owns tensor memory,
+//     warps 2-5  softmax: ONE THREAD PER QUERY ROW (tensor-memory lane = row), so maxima and
+//                sums need no shuffles.
+//   per key tile j:   S_j = Q K_j^T      128 x 64 x 128, both operands K-major from shared
+//                                        memory, S in tensor memory (two buffers)
+//                     P_j = 2^(S_j c - m) in registers, written as bf16 to shared memory in
+//                                        the K-major swizzled layout an A operand has
+//                     O  += P_j V_j       128 x 128 x 64, V MN-major exactly as TMA wrote the
+//                                        cache block, O accumulating in tensor memory
+//   The exponent's reference m trails the true running maximum: it is moved (and O and the
+//   row sum rescaled, in tensor memory) only when the maximum has grown by more than 2^8,
+//   so most tiles cost a row nothing but 64 exponentials. The MMA lane runs ahead: S_{j+1}
+//   is issued before P_j V_j, so the tensor cores work on the next scores while the softmax
+//   warps exponentiate the current ones; two blocks share an SM (256 of the 512 columns of
+//   tensor memory each) and fill each other's gaps.
+//
+// Scores, maxima, exponentials, sums and the output are fp32; P is rounded to bf16 for
+// P.V, as keys and values are stored. Every mbarrier wait is bounded; no cluster, no
+// multicast. The reference's prefill shape is 16 queries x 1 head per block on CUDA cores
+// (`src/core_kernels/attention.cu:449-746, 910-950`).
+#include "common.cuh"
+#include "mma.cuh"
+#include "tcgen05.cuh"
+#include "tma.cuh"
+
+namespace {
+
+constexpr int D = 128;               // head size
+constexpr int KT = kCacheBlock;      // keys per tile
+constexpr int QT = 128;              // queries per tile = tensor-memory lanes
+constexpr int kStages = 2;
+constexpr int kThreads = 192;
+constexpr int kQBytes = QT * D * 2;              // two boxes of [128 x 64]
+constexpr int kTileBytes = KT * D * 2;           // K or V: two boxes of [64 x 64]
+constexpr int kStageBytes = 2 * kTileBytes;
+constexpr int kPBytes = QT * KT * 2;             // one P buffer [128 x 64] bf16
+constexpr int kSmemBytes = kQBytes + kStages * kStageBytes + kPBytes + 256;    // 112.25 KB
+constexpr uint32_t kTmemCols = 256;              // S: 2 x 64, O: 128
+constexpr uint32_t kSCol = 0, kOCol = 128;
+constexpr float kLazy = 8.f;                     // move the reference when the maximum grew by 2^8
+
+struct Barriers {
+  uint64_t q_full;
+  uint64_t kv_full[kStages], kv_empty[kStages];
+  uint64_t s_full[2], s_free[2];
+  uint64_t p_full;       // the P tile is in shared memory (and stale value rows are zeroed)
+  uint64_t pv_done;      // P_j V_j has been added to O: P may be overwritten, O may be rescaled
+  uint32_t tmem;
+};
+
+// V tile as the B operand of P.V: N (head dims) contiguous, 64 per 128-byte row, the next
+// 64 dims one box (8 KB) further; 8 keys per 1024-byte swizzle group.
+__device__ __forceinline__ uint64_t smem_desc_mn_major_sw128(uint32_t addr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((addr & 0x3FFFF) >> 4);
+  d |= static_cast<uint64_t>((KT * 128) >> 4) << 16;
+  d |= static_cast<uint64_t>(1024 >> 4) << 32;
+  d |= static_cast<uint64_t>(1) << 46;
+  d |= static_cast<uint64_t>(2) << 61;
+  return d;
+}
+
+// q_tiles[i] = {sequence, first token row of the tile in the step, rows <= 128, position of the first row}
+__global__ void __launch_bounds__(kThreads, 2)
+prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap q_map,
+                            const __grid_constant__ CUtensorMap k_map,
+                            const __grid_constant__ CUtensorMap v_map,
+                            __nv_bfloat16* __restrict__ out, const int4* __restrict__ q_tiles,
+                            const int32_t* __restrict__ seq_lens,
+                            const int32_t* __restrict__ block_table, int max_blocks, int heads,
+                            int kv_heads, float scale_log2e, int window, int* __restrict__ error) {
+  // Exactly 112.25 KB, so that two blocks fit an SM: no slack for aligning by hand. The
+  // swizzled tiles need a 1024-byte aligned base; a block that does not get one says so.
+  extern __shared__ __align__(1024) uint8_t smem[];
+  if (tma::smem_u32(smem) & 1023) {
+    if (threadIdx.x == 0 && error) atomicCAS(error, 0, 499);
+    return;
+  }
+  uint8_t* q_s = smem;
+  uint8_t* kv_s = q_s + kQBytes;
+  uint8_t* p_s = kv_s + kStages * kStageBytes;
+  Barriers* bar = reinterpret_cast<Barriers*>(p_s + kPBytes);
+
+  const int4 tile = q_tiles[blockIdx.x];
+  const int b = tile.x, row0 = tile.y, rows = tile.z, pos0 = tile.w;
+  const int h = blockIdx.y;
+  const int g = h / (heads / kv_heads);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kv_len = seq_lens[b];
+  const int last_pos = pos0 + rows - 1;
+  const int first_key = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
+  const int t0 = first_key / KT;
+  const int n = last_pos / KT + 1 - t0;          // key tiles t0 .. t0 + n - 1
+
+  if (threadIdx.x == 0) {
+    tma::mbar_init(&bar->q_full, 1);
+    for (int s = 0; s < kStages; ++s) {
+      tma::mbar_init(&bar->kv_full[s], 1);
+      tma::mbar_init(&bar->kv_empty[s], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      tma::mbar_init(&bar->s_full[i], 1);
+      tma::mbar_init(&bar->s_free[i], QT);
+    }
+    tma::mbar_init(&bar->p_full, QT);
+    tma::mbar_init(&bar->pv_done, 1);
+    tma::fence_barrier_init();
+  }
+  if (warp == 1) tc::tmem_alloc(&bar->tmem, kTmemCols);
+  tc::fence_before_sync();
+  __syncthreads();
+  tc::fence_after_sync();
+  const uint32_t tmem = bar->tmem;
+
+  if (warp == 0) {
+    // ---- TMA ----------------------------------------------------------------------------
+    if (lane == 0) {
+      tma::prefetch_map(&q_map);
+      tma::prefetch_map(&k_map);
+      tma::prefetch_map(&v_map);
+      tma::mbar_expect_tx(&bar->q_full, kQBytes);
+      tma::load_2d(q_s, &q_map, h * D, row0, &bar->q_full);
+      tma::load_2d(q_s + QT * 128, &q_map, h * D + 64, row0, &bar->q_full);
+      for (int j = 0; j < n; ++j) {
+        const int stage = j % kStages;
+        if (j >= kStages &&
+            !tma::mbar_wait(&bar->kv_empty[stage], ((j / kStages) - 1) & 1, error, 401))
+          break;
+        const int block = block_table[(long long)b * max_blocks + t0 + j];
+        const int krow0 = (block * kv_heads + g) * KT;
+        uint8_t* dst = kv_s + stage * kStageBytes;
+        tma::mbar_expect_tx(&bar->kv_full[stage], kStageBytes);
+        tma::load_2d(dst, &k_map, 0, krow0, &bar->kv_full[stage]);
+        tma::load_2d(dst + KT * 128, &k_map, 64, krow0, &bar->kv_full[stage]);
+        tma::load_2d(dst + kTileBytes, &v_map, 0, krow0, &bar->kv_full[stage]);
+        tma::load_2d(dst + kTileBytes + KT * 128, &v_map, 64, krow0, &bar->kv_full[stage]);
+      }
+    }
+  } else if (warp == 1) {
+    // ---- MMA issue -------------------------------------------------------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = tc::idesc_bf16_f32(QT, KT);                    // K-major both
+      constexpr uint32_t idesc_pv = tc::idesc_bf16_f32(QT, D) | (1u << 16);        // B MN-major
+      bool ok = tma::mbar_wait(&bar->q_full, 0, error, 402);
+      const uint32_t q_addr = tma::smem_u32(q_s);
+      auto issue_pv = [&](int i) {
+        const int stage = i % kStages;
+        if (!tma::mbar_wait(&bar->p_full, i & 1, error, 403)) return false;
+        tc::fence_after_sync();
+        const uint32_t p_addr = tma::smem_u32(p_s);
+        const uint32_t v_addr = tma::smem_u32(kv_s + stage * kStageBytes + kTileBytes);
+#pragma unroll
+        for (int k = 0; k < KT / 16; ++k)
+          tc::mma_ss(tmem + kOCol, tc::smem_desc_k_major_sw128(p_addr + k * 32),
+                     smem_desc_mn_major_sw128(v_addr + k * 2048), idesc_pv, i > 0 || k > 0);
+        tc::commit(&bar->pv_done);
+        tc::commit(&bar->kv_empty[stage]);
+        return true;
+      };
+      for (int j = 0; j < n && ok; ++j) {
+        const int bj = j & 1, stage = j % kStages;
+        ok = tma::mbar_wait(&bar->kv_full[stage], (j / kStages) & 1, error, 405);
+        if (ok && j >= 2) ok = tma::mbar_wait(&bar->s_free[bj], ((j >> 1) - 1) & 1, error, 406);
+        if (!ok) break;
+        tc::fence_after_sync();
+        const uint32_t k_addr = tma::smem_u32(kv_s + stage * kStageBytes);
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k)
+          tc::mma_ss(tmem + kSCol + bj * KT,
+                     tc::smem_desc_k_major_sw128(q_addr + (k >> 2) * (QT * 128) + (k & 3) * 32),
+                     tc::smem_desc_k_major_sw128(k_addr + (k >> 2) * (KT * 128) + (k & 3) * 32),
+                     idesc_s, k > 0);
+        tc::commit(&bar->s_full[bj]);
+        if (j >= 1) ok = issue_pv(j - 1);
+      }
+      if (ok && n > 0) issue_pv(n - 1);
+    }
+  } else {
+    // ---- softmax: one thread per query row ---------------------------------------------------
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;                         // row of the tile = tensor-memory lane
+    const int pos = pos0 + r;
+    const uint32_t lane_base = tmem + (static_cast<uint32_t>(quarter * 32) << 16);
+    float m_true = -INFINITY;      // running maximum of the scaled scores
+    float m_ref = -INFINITY;       // what the exponentials, the row sum and O are relative to
+    float l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n; ++j) {
+      const int bj = j & 1;
+      if (!tma::mbar_wait(&bar->s_full[bj], (j >> 1) & 1, error, 407)) { ok = false; break; }
+      tc::fence_after_sync();
+      float s[KT];
+#pragma unroll
+      for (int c = 0; c < KT; c += 16) {
+        float v[16];
+        tc::ld_32x32b_x16(lane_base + kSCol + bj * KT + c, v);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) s[c + i] = v[i];
+      }
+      tc::fence_before_sync();
+      tma::mbar_arrive(&bar->s_free[bj]);
+      const int key0 = (t0 + j) * KT;
+      const bool needs_mask = key0 + KT - 1 > pos0 || (window > 0 && key0 < last_pos - window + 1);
+      float big = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < KT; ++c) {
+        if (needs_mask) {
+          const int key = key0 + c;
+          const bool seen = key <= pos && (window <= 0 || key > pos - window);
+          s[c] = seen ? s[c] : -INFINITY;
+        }
+        big = fmaxf(big, s[c]);
+      }
+      m_true = fmaxf(m_true, big * scale_log2e);
+      // P_{j-1} V_{j-1} must be done before P is overwritten and before O is touched
+      if (j >= 1 && !tma::mbar_wait(&bar->pv_done, (j - 1) & 1, error, 408)) { ok = false; break; }
+      const bool move = m_true > m_ref + kLazy;      // (also true the first time a key is seen)
+      if (__any_sync(0xffffffffu, move)) {
+        const float factor = move ? mma::exp2_fast(m_ref - m_true) : 1.f;   // 0 when m_ref = -inf
+        if (j >= 1) {
+          tc::fence_after_sync();
+#pragma unroll
+          for (int c = 0; c < D; c += 16) {
+            float v[16];
+            tc::ld_32x32b_x16(lane_base + kOCol + c, v);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) v[i] *= factor;
+            tc::st_32x32b_x16(lane_base + kOCol + c, v);
+          }
+          tc::fence_before_sync();
+        }
+        if (move) {
+          l *= factor;
+          m_ref = m_true;
+        }
+      }
+      const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
+      float sum = 0.f;
+      // P row, bf16, into the swizzled K-major layout of an A operand: 8 chunks of 8 keys
+      uint8_t* p_row = p_s + r * 128;
+#pragma unroll
+      for (int ch = 0; ch < KT / 8; ++ch) {
+        uint32_t packed[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float p0 = mma::exp2_fast(fmaf(s[ch * 8 + 2 * i], scale_log2e, -m_use));
+          const float p1 = mma::exp2_fast(fmaf(s[ch * 8 + 2 * i + 1], scale_log2e, -m_use));
+          sum += p0 + p1;
+          packed[i] = mma::pack_bf16(p0, p1);
+        }
+        *reinterpret_cast<uint4*>(p_row + ((ch ^ (r & 7)) << 4)) =
+            make_uint4(packed[0], packed[1], packed[2], packed[3]);
+      }
+      l += sum;
+      // the sequence's last block: value rows past its end are stale; zero them before P.V
+      const int valid = kv_len - key0;
+      if (valid < KT) {
+        uint8_t* vt = kv_s + ((j % kStages) * kStageBytes) + kTileBytes;
+        for (int row = valid + (r >> 4); row < KT; row += QT / 16)
+          *reinterpret_cast<uint4*>(vt + ((r & 15) >> 3) * (KT * 128) + row * 128 + ((r & 7) << 4)) =
+              make_uint4(0, 0, 0, 0);
+      }
+      tma::fence_proxy_async();
+      tc::fence_before_sync();
+      tma::mbar_arrive(&bar->p_full);
+    }
+    if (ok && n > 0 && tma::mbar_wait(&bar->pv_done, (n - 1) & 1, error, 410)) {
+      tc::fence_after_sync();
+      const float inv = 1.f / l;
+      __nv_bfloat16* dst = out + ((long long)(row0 + r) * heads + h) * D;
+#pragma unroll
+      for (int c = 0; c < D; c += 16) {
+        float v[16];
+        tc::ld_32x32b_x16(lane_base + kOCol + c, v);
+        if (r < rows) {
+          uint32_t w[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) w[i] = mma::pack_bf16(v[2 * i] * inv, v[2 * i + 1] * inv);
+          *reinterpret_cast<uint4*>(dst + c) = make_uint4(w[0], w[1], w[2], w[3]);
+          *reinterpret_cast<uint4*>(dst + c + 8) = make_uint4(w[4], w[5], w[6], w[7]);
+        }
+      }
+    }
+    tc::fence_before_sync();
+  }
+  __syncthreads();
+  if (warp == 1) {
+    tc::fence_after_sync();
+    tc::tmem_dealloc(tmem, kTmemCols);
+  }
+}
+
+__device__ int g_error;
+
+}  // namespace
+
+// A TMA descriptor of the step's fused projection buffer [tokens, width] (bf16), read in boxes
+// of 128 rows x 64 columns; `map` points to 128 bytes on the host.
+SAKV_EXPORT int sakv_prefill_attention_tc_qmap(void* map, const void* qkv, long long tokens,
+                                               long long width, long long row_stride) {
+  if (tokens <= 0 || width <= 0 || (width % 8) || (row_stride % 8)) return cudaErrorInvalidValue;
+  return tma::make_map_bf16_2d(reinterpret_cast<CUtensorMap*>(map), qkv, (uint64_t)tokens,
+                               (uint64_t)width, (uint64_t)row_stride * 2, QT, 64);
+}
+
+SAKV_EXPORT int sakv_prefill_attention_tc(const void* q_map, const void* k_map, const void* v_map,
+                                          void* out, const int32_t* q_tiles, int n_tiles,
+                                          const int32_t* seq_lens, const int32_t* block_table,
+                                          int max_blocks, int heads, int kv_heads, int head_dim,
+                                          float scale, int window, cudaStream_t stream) {
+  if (n_tiles < 0 || heads <= 0 || kv_heads <= 0 || heads % kv_heads || max_blocks <= 0 ||
+      heads > 65535 || head_dim != D || (reinterpret_cast<uintptr_t>(q_tiles) & 15) ||
+      (reinterpret_cast<uintptr_t>(out) & 15))
+    return cudaErrorInvalidValue;
+  if (n_tiles == 0) return 0;
+  static bool configured = false;
+  int* error = nullptr;
+  if (cudaGetSymbolAddress(reinterpret_cast<void**>(&error), g_error) != cudaSuccess)
+    return cudaErrorInvalidValue;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(prefill_attention_tc_kernel,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    if (e == cudaSuccess)      // all of the SM's memory as shared memory: two blocks fit
+      e = cudaFuncSetAttribute(prefill_attention_tc_kernel,
+                               cudaFuncAttributePreferredSharedMemoryCarveout,
+                               cudaSharedmemCarveoutMaxShared);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    configured = true;
+  }
+  prefill_attention_tc_kernel<<<dim3(n_tiles, heads), kThreads, kSmemBytes, stream>>>(
+      *(const CUtensorMap*)q_map, *(const CUtensorMap*)k_map, *(const CUtensorMap*)v_map,
+      (__nv_bfloat16*)out, (const int4*)q_tiles, seq_lens, block_table, max_blocks, heads,
+      kv_heads, scale * 1.4426950408889634f, window, error);
+  return launch_status();
+}
+
+SAKV_EXPORT int sakv_prefill_attention_tc_error(int* value) {
+  return static_cast<int>(cudaMemcpyFromSymbol(value, g_error, sizeof(int)));
+}

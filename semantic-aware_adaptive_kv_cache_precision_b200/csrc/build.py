@@ -42,6 +42,7 @@ LIBRARIES = {
     "sampling": "sampling.cu",
     "attention_decode": "attention_decode.cu",
     "attention_prefill": "attention_prefill.cu",
+    "attention_prefill_tc": "attention_prefill_tc.cu",
     "gemm_tc": "gemm_tc.cu",
 }
 

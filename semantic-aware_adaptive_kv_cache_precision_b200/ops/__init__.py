@@ -14,11 +14,12 @@ from ._lib import (BF16, CACHE_BLOCK, F32, KernelError, call, dtype_code, plain_
                    require_cuda)
 from .linear import gated_up, linear
 from . import gemm_tc
-from .attention import (attention_decode, attention_prefill, decode_splits, fast_path_takes,
-                        kernel_errors)
+from .attention import (attention_decode, attention_prefill, attention_prefill_tc, decode_splits,
+                        fast_path_takes, kernel_errors, tc_prefill_takes)
 
 __all__ = ["CACHE_BLOCK", "KernelError", "embed", "rms_norm", "rope_store", "attention_plain",
-           "attention_decode", "attention_prefill", "decode_splits", "fast_path_takes",
+           "attention_decode", "attention_prefill", "attention_prefill_tc", "tc_prefill_takes",
+           "decode_splits", "fast_path_takes",
            "kernel_errors", "gated_silu", "gated_up", "gemm_tc", "add_into", "linear", "choose"]
 
 

@@ -34,6 +34,8 @@ SIGNATURES = {
                               [P, P, P, L, P, P, I, P, P, P, I, I, I, I, I, F, I, P]),
     "sakv_prefill_attention": ("attention_prefill",
                                [P, P, P, L, P, P, I, P, P, I, I, I, I, F, I, P]),
+    "sakv_prefill_attention_tc": ("attention_prefill_tc",
+                                  [P, P, P, P, P, I, P, P, I, I, I, I, F, I, P]),
     "sakv_gemm_tc": ("gemm_tc", [P, P, I, I, I, I, I, I, I, P, I, P, L, P]),
 }
 
@@ -43,6 +45,8 @@ PLAIN_SIGNATURES = {
     "sakv_decode_attention_map": ("attention_decode", [P, P, L, I, I]),
     "sakv_decode_attention_error": ("attention_decode", [P]),
     "sakv_prefill_attention_error": ("attention_prefill", [P]),
+    "sakv_prefill_attention_tc_error": ("attention_prefill_tc", [P]),
+    "sakv_prefill_attention_tc_qmap": ("attention_prefill_tc", [P, P, L, L, L]),
     "sakv_gemm_tc_map": ("gemm_tc", [P, P, L, L, L, I]),
     "sakv_gemm_tc_splits": ("gemm_tc", [I, I]),
     "sakv_gemm_tc_max_clusters": ("gemm_tc", [I, I, I]),

@@ -97,10 +97,45 @@ def attention_prefill(qkv: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.T
     return out
 
 
+def tc_prefill_takes(dtype: torch.dtype, heads: int, kv_heads: int, head_dim: int) -> bool:
+    """Whether the tcgen05 prefill kernel takes these sizes (head size 128)."""
+    return dtype == torch.bfloat16 and head_dim == 128 and heads % kv_heads == 0
+
+
+def attention_prefill_tc(qkv: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                         q_tiles: torch.Tensor, seq_lens: torch.Tensor, block_table: torch.Tensor,
+                         heads: int, kv_heads: int, head_dim: int, scale: float,
+                         window) -> torch.Tensor:
+    """The tcgen05 prefill kernel. `q_tiles`: int32 [n, 4] = (sequence, first token row,
+    rows <= 128, first position)."""
+    require_cuda(qkv, k_cache, v_cache, q_tiles, seq_lens, block_table)
+    if not tc_prefill_takes(qkv.dtype, heads, kv_heads, head_dim):
+        raise KernelError("attention_prefill_tc: sizes not taken (bf16, head_dim 128)")
+    if qkv.stride(1) != 1 or qkv.shape[1] < heads * head_dim or (qkv.stride(0) % 8) \
+            or qkv.data_ptr() % 16:
+        raise KernelError("attention_prefill_tc: qkv must be [T, >= heads * head_dim] with rows "
+                          "a multiple of 16 bytes apart")
+    if q_tiles.dtype != torch.int32 or q_tiles.dim() != 2 or q_tiles.shape[1] != 4 \
+            or not q_tiles.is_contiguous():
+        raise KernelError("attention_prefill_tc: q_tiles must be int32 [n, 4]")
+    raw = ctypes.create_string_buffer(128 + 64)
+    q_map = (ctypes.addressof(raw) + 63) & ~63
+    code = plain_function("sakv_prefill_attention_tc_qmap")(q_map, qkv.data_ptr(), qkv.shape[0],
+                                                            qkv.shape[1], qkv.stride(0))
+    if code != 0:
+        raise KernelError(f"could not make a TMA descriptor for the queries (error {code})")
+    out = torch.empty((qkv.shape[0], heads * head_dim), dtype=torch.bfloat16, device=qkv.device)
+    call("sakv_prefill_attention_tc", q_map, tensor_map(k_cache), tensor_map(v_cache), ptr(out),
+         ptr(q_tiles), q_tiles.shape[0], ptr(seq_lens), ptr(block_table), block_table.shape[1],
+         heads, kv_heads, head_dim, float(scale), int(window) if window else 0)
+    return out
+
+
 def kernel_errors() -> dict:
     """Error words left by waits that gave up (0 = none). Synchronises the device."""
     out = {}
-    for name in ("sakv_decode_attention_error", "sakv_prefill_attention_error"):
+    for name in ("sakv_decode_attention_error", "sakv_prefill_attention_error",
+                 "sakv_prefill_attention_tc_error"):
         value = ctypes.c_int(0)
         code = plain_function(name)(ctypes.addressof(value))
         out[name] = value.value if code == 0 else -code

@@ -86,14 +86,20 @@ class GQAAttention(Part):
     def attend(self, qkv, step, view):
         """Tensor-core kernels where they take the sizes (bf16, head_dim 64 or 128, up
         to 16 query heads per KV head): the split-key decode kernel when every
-        sequence brings one token, the causal prefill kernel otherwise. Everything
-        else, and the whole fp32 path, runs the plain kernel."""
+        sequence brings one token; otherwise the causal prefill kernels, tcgen05 for
+        head size 128 and mma.sync for 64. Everything else, and the whole fp32 path,
+        runs the plain kernel."""
         s = self.spec
         if ops.fast_path_takes(qkv.dtype, s.heads, s.kv_heads, s.head_dim):
             if step.is_decode:
                 return ops.attention_decode(qkv, view.keys, view.values, step.seq_lens,
                                             view.block_table, s.heads, s.kv_heads, s.head_dim,
                                             s.scale, s.window, step.max_len_bound or step.max_len)
+            if ops.tc_prefill_takes(qkv.dtype, s.heads, s.kv_heads, s.head_dim) \
+                    and step.q_tiles_wide is not None:
+                return ops.attention_prefill_tc(qkv, view.keys, view.values, step.q_tiles_wide,
+                                                step.seq_lens, view.block_table, s.heads,
+                                                s.kv_heads, s.head_dim, s.scale, s.window)
             return ops.attention_prefill(qkv, view.keys, view.values, step.q_tiles,
                                          step.seq_lens, view.block_table, s.heads, s.kv_heads,
                                          s.head_dim, s.scale, s.window)

@@ -389,8 +389,7 @@ def test_attention_decode_kernel(heads, kv_heads, d, window, splits):
     got = ops.attention_decode(qkv, k_cache, v_cache, dev(lengths, torch.int32),
                                dev(table, torch.int32), heads, kv_heads, d, scale, window,
                                max(lengths), splits=splits)
-    assert ops.kernel_errors() == {"sakv_decode_attention_error": 0,
-                                   "sakv_prefill_attention_error": 0}
+    assert all(v == 0 for v in ops.kernel_errors().values())
     q = host(qkv)[:, :heads * d].reshape(B, heads, d)
     for i, n in enumerate(lengths):
         first = max(0, n - window) if window else 0
@@ -543,3 +542,46 @@ def test_vector_paths_of_the_elementwise_kernels(dtype):
     want = host(acc) + host(y)
     ops.add_into(acc, y)
     np.testing.assert_allclose(host(acc), want, rtol=0, atol=1e-6)
+
+
+@pytest.mark.parametrize("heads,kv_heads,window", [(12, 2, None), (4, 4, None), (7, 1, 200),
+                                                   (6, 3, 64)])
+def test_attention_prefill_tcgen05_kernel(heads, kv_heads, window):
+    d = 128
+    rng = np.random.default_rng(heads + (window or 0))
+    cases = [(0, 150), (0, 128), (299, 1), (64, 2), (100, 130), (0, 1), (37, 91), (600, 300)]
+    lengths = [a + n for a, n in cases]
+    k_cache, v_cache, table = paged_case(rng, lengths, kv_heads, d)
+    T = sum(n for _, n in cases)
+    width = (heads + 2 * kv_heads) * d
+    qkv = dev(rng.standard_normal((T, width)), torch.bfloat16)
+    tiles, row = [], 0
+    for i, (a, n) in enumerate(cases):
+        for s in range(0, n, 128):
+            tiles.append((i, row + s, min(128, n - s), a + s))
+        row += n
+    scale = d ** -0.5
+    got = ops.attention_prefill_tc(qkv, k_cache, v_cache, dev(tiles, torch.int32),
+                                   dev(lengths, torch.int32), dev(table, torch.int32), heads,
+                                   kv_heads, d, scale, window)
+    assert ops.kernel_errors()["sakv_prefill_attention_tc_error"] == 0
+    q = host(qkv)[:, :heads * d].reshape(T, heads, d)
+    row = 0
+    for i, (a, n) in enumerate(cases):
+        kk = sequence_kv(k_cache, table[i], lengths[i])
+        vv = sequence_kv(v_cache, table[i], lengths[i])
+        for t in range(n):
+            want = attention_reference(q[row + t], kk, vv, a + t, heads, kv_heads, scale, window)
+            np.testing.assert_allclose(host(got[row + t]).reshape(heads, d), want, rtol=0,
+                                       atol=1.5e-2, err_msg=f"case {i}, token {t}")
+        row += n
+    # and its twin on the mma.sync path agrees
+    tiles64, row = [], 0
+    for i, (a, n) in enumerate(cases):
+        for s in range(0, n, 64):
+            tiles64.append((i, row + s, min(64, n - s), a + s))
+        row += n
+    twin = ops.attention_prefill(qkv, k_cache, v_cache, dev(tiles64, torch.int32),
+                                 dev(lengths, torch.int32), dev(table, torch.int32), heads,
+                                 kv_heads, d, scale, window)
+    np.testing.assert_allclose(host(got), host(twin), rtol=0, atol=2e-2)
