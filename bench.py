@@ -293,11 +293,12 @@ def kernel_case(name: str) -> int:
         k = torch.randn(n // 64, G, 64, d, device=dev, dtype=torch.bfloat16)
         v = torch.randn_like(k)
         table = torch.arange(n // 64, dtype=torch.int32, device=dev).view(1, -1).contiguous()
-        tiles = torch.tensor([(0, s, 64, s) for s in range(n - 64, -1, -64)], dtype=torch.int32,
+        tiles = torch.tensor([(0, s, 128, s) for s in range(n - 128, -1, -128)], dtype=torch.int32,
                              device=dev)
         lens = torch.tensor([n], dtype=torch.int32, device=dev)
         qkv = torch.randn(n, (A + 2 * G) * d, device=dev, dtype=torch.bfloat16)
-        run = lambda i: ops.attention_prefill(qkv, k, v, tiles, lens, table, A, G, d, d ** -0.5, None)
+        run = lambda i: ops.attention_prefill_tc(qkv, k, v, tiles, lens, table, A, G, d, d ** -0.5,
+                                                 None)
     else:
         raise SystemExit(f"unknown kernel case {name}")
     for i in range(4):

@@ -49,7 +49,8 @@ constexpr float kLazy = 8.f;                     // move the reference when the 
 
 struct Barriers {
   uint64_t q_full;
-  uint64_t kv_full[kStages], kv_empty[kStages];
+  uint64_t k_full[kStages], k_empty[kStages];     // keys: free again as soon as S_j is done
+  uint64_t v_full[kStages], v_empty[kStages];     // values: free once P_j V_j is done
   uint64_t s_full[2], s_free[2];
   uint64_t p_full;       // the P tile is in shared memory (and stale value rows are zeroed)
   uint64_t pv_done;      // P_j V_j has been added to O: P may be overwritten, O may be rescaled
@@ -89,9 +90,11 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap q_map,
   uint8_t* p_s = kv_s + kStages * kStageBytes;
   Barriers* bar = reinterpret_cast<Barriers*>(p_s + kPBytes);
 
-  const int4 tile = q_tiles[blockIdx.x];
+  // blockIdx.x = head, blockIdx.y = tile: the tiles come heaviest first, so the blocks that
+  // start first are the long ones of every head, and the short ones fill in behind them
+  const int4 tile = q_tiles[blockIdx.y];
   const int b = tile.x, row0 = tile.y, rows = tile.z, pos0 = tile.w;
-  const int h = blockIdx.y;
+  const int h = blockIdx.x;
   const int g = h / (heads / kv_heads);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int kv_len = seq_lens[b];
@@ -103,8 +106,10 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap q_map,
   if (threadIdx.x == 0) {
     tma::mbar_init(&bar->q_full, 1);
     for (int s = 0; s < kStages; ++s) {
-      tma::mbar_init(&bar->kv_full[s], 1);
-      tma::mbar_init(&bar->kv_empty[s], 1);
+      tma::mbar_init(&bar->k_full[s], 1);
+      tma::mbar_init(&bar->k_empty[s], 1);
+      tma::mbar_init(&bar->v_full[s], 1);
+      tma::mbar_init(&bar->v_empty[s], 1);
     }
     for (int i = 0; i < 2; ++i) {
       tma::mbar_init(&bar->s_full[i], 1);
@@ -129,19 +134,26 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap q_map,
       tma::mbar_expect_tx(&bar->q_full, kQBytes);
       tma::load_2d(q_s, &q_map, h * D, row0, &bar->q_full);
       tma::load_2d(q_s + QT * 128, &q_map, h * D + 64, row0, &bar->q_full);
+      // Keys and values have rings of their own: a key stage is free again as soon as its
+      // scores are computed, long before its values are used, so the next keys are already
+      // on their way while the softmax of this tile runs.
       for (int j = 0; j < n; ++j) {
         const int stage = j % kStages;
-        if (j >= kStages &&
-            !tma::mbar_wait(&bar->kv_empty[stage], ((j / kStages) - 1) & 1, error, 401))
-          break;
         const int block = block_table[(long long)b * max_blocks + t0 + j];
         const int krow0 = (block * kv_heads + g) * KT;
         uint8_t* dst = kv_s + stage * kStageBytes;
-        tma::mbar_expect_tx(&bar->kv_full[stage], kStageBytes);
-        tma::load_2d(dst, &k_map, 0, krow0, &bar->kv_full[stage]);
-        tma::load_2d(dst + KT * 128, &k_map, 64, krow0, &bar->kv_full[stage]);
-        tma::load_2d(dst + kTileBytes, &v_map, 0, krow0, &bar->kv_full[stage]);
-        tma::load_2d(dst + kTileBytes + KT * 128, &v_map, 64, krow0, &bar->kv_full[stage]);
+        if (j >= kStages &&
+            !tma::mbar_wait(&bar->k_empty[stage], ((j / kStages) - 1) & 1, error, 401))
+          break;
+        tma::mbar_expect_tx(&bar->k_full[stage], kTileBytes);
+        tma::load_2d(dst, &k_map, 0, krow0, &bar->k_full[stage]);
+        tma::load_2d(dst + KT * 128, &k_map, 64, krow0, &bar->k_full[stage]);
+        if (j >= kStages &&
+            !tma::mbar_wait(&bar->v_empty[stage], ((j / kStages) - 1) & 1, error, 411))
+          break;
+        tma::mbar_expect_tx(&bar->v_full[stage], kTileBytes);
+        tma::load_2d(dst + kTileBytes, &v_map, 0, krow0, &bar->v_full[stage]);
+        tma::load_2d(dst + kTileBytes + KT * 128, &v_map, 64, krow0, &bar->v_full[stage]);
       }
     }
   } else if (warp == 1) {
@@ -154,6 +166,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap q_map,
       auto issue_pv = [&](int i) {
         const int stage = i % kStages;
         if (!tma::mbar_wait(&bar->p_full, i & 1, error, 403)) return false;
+        if (!tma::mbar_wait(&bar->v_full[stage], (i / kStages) & 1, error, 412)) return false;
         tc::fence_after_sync();
         const uint32_t p_addr = tma::smem_u32(p_s);
         const uint32_t v_addr = tma::smem_u32(kv_s + stage * kStageBytes + kTileBytes);
@@ -162,12 +175,12 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap q_map,
           tc::mma_ss(tmem + kOCol, tc::smem_desc_k_major_sw128(p_addr + k * 32),
                      smem_desc_mn_major_sw128(v_addr + k * 2048), idesc_pv, i > 0 || k > 0);
         tc::commit(&bar->pv_done);
-        tc::commit(&bar->kv_empty[stage]);
+        tc::commit(&bar->v_empty[stage]);
         return true;
       };
       for (int j = 0; j < n && ok; ++j) {
         const int bj = j & 1, stage = j % kStages;
-        ok = tma::mbar_wait(&bar->kv_full[stage], (j / kStages) & 1, error, 405);
+        ok = tma::mbar_wait(&bar->k_full[stage], (j / kStages) & 1, error, 405);
         if (ok && j >= 2) ok = tma::mbar_wait(&bar->s_free[bj], ((j >> 1) - 1) & 1, error, 406);
         if (!ok) break;
         tc::fence_after_sync();
@@ -179,6 +192,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap q_map,
                      tc::smem_desc_k_major_sw128(k_addr + (k >> 2) * (KT * 128) + (k & 3) * 32),
                      idesc_s, k > 0);
         tc::commit(&bar->s_full[bj]);
+        tc::commit(&bar->k_empty[stage]);
         if (j >= 1) ok = issue_pv(j - 1);
       }
       if (ok && n > 0) issue_pv(n - 1);
@@ -263,6 +277,10 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap q_map,
       // the sequence's last block: value rows past its end are stale; zero them before P.V
       const int valid = kv_len - key0;
       if (valid < KT) {
+        if (!tma::mbar_wait(&bar->v_full[j % kStages], (j / kStages) & 1, error, 413)) {
+          ok = false;
+          break;
+        }
         uint8_t* vt = kv_s + ((j % kStages) * kStageBytes) + kTileBytes;
         for (int row = valid + (r >> 4); row < KT; row += QT / 16)
           *reinterpret_cast<uint4*>(vt + ((r & 15) >> 3) * (KT * 128) + row * 128 + ((r & 7) << 4)) =
@@ -316,8 +334,8 @@ SAKV_EXPORT int sakv_prefill_attention_tc(const void* q_map, const void* k_map, 
                                           const int32_t* seq_lens, const int32_t* block_table,
                                           int max_blocks, int heads, int kv_heads, int head_dim,
                                           float scale, int window, cudaStream_t stream) {
-  if (n_tiles < 0 || heads <= 0 || kv_heads <= 0 || heads % kv_heads || max_blocks <= 0 ||
-      heads > 65535 || head_dim != D || (reinterpret_cast<uintptr_t>(q_tiles) & 15) ||
+  if (n_tiles < 0 || n_tiles > 65535 || heads <= 0 || kv_heads <= 0 || heads % kv_heads ||
+      max_blocks <= 0 || head_dim != D || (reinterpret_cast<uintptr_t>(q_tiles) & 15) ||
       (reinterpret_cast<uintptr_t>(out) & 15))
     return cudaErrorInvalidValue;
   if (n_tiles == 0) return 0;
@@ -335,7 +353,7 @@ SAKV_EXPORT int sakv_prefill_attention_tc(const void* q_map, const void* k_map, 
     if (e != cudaSuccess) return static_cast<int>(e);
     configured = true;
   }
-  prefill_attention_tc_kernel<<<dim3(n_tiles, heads), kThreads, kSmemBytes, stream>>>(
+  prefill_attention_tc_kernel<<<dim3(heads, n_tiles), kThreads, kSmemBytes, stream>>>(
       *(const CUtensorMap*)q_map, *(const CUtensorMap*)k_map, *(const CUtensorMap*)v_map,
       (__nv_bfloat16*)out, (const int4*)q_tiles, seq_lens, block_table, max_blocks, heads,
       kv_heads, scale * 1.4426950408889634f, window, error);
