@@ -293,11 +293,10 @@ def kernel_case(name: str) -> int:
         k = torch.randn(n // 64, G, 64, d, device=dev, dtype=torch.bfloat16)
         v = torch.randn_like(k)
         table = torch.arange(n // 64, dtype=torch.int32, device=dev).view(1, -1).contiguous()
-        tiles = torch.tensor([(0, s, 128, s) for s in range(n - 128, -1, -128)], dtype=torch.int32,
-                             device=dev)
+        plan = ops.upload_wide_plan([0], [n], A, None, dev)
         lens = torch.tensor([n], dtype=torch.int32, device=dev)
         qkv = torch.randn(n, (A + 2 * G) * d, device=dev, dtype=torch.bfloat16)
-        run = lambda i: ops.attention_prefill_tc(qkv, k, v, tiles, lens, table, A, G, d, d ** -0.5,
+        run = lambda i: ops.attention_prefill_tc(qkv, k, v, *plan, lens, table, A, G, d, d ** -0.5,
                                                  None)
     else:
         raise SystemExit(f"unknown kernel case {name}")

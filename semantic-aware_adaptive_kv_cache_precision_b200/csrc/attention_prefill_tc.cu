@@ -69,12 +69,27 @@ __device__ __forceinline__ uint64_t smem_desc_mn_major_sw128(uint32_t addr) {
   return d;
 }
 
-// q_tiles[i] = {sequence, first token row of the tile in the step, rows <= 128, position of the first row}
+// One block's work: a query tile and a run of its sequence's key tiles. A tile with many key
+// tiles may be dealt to several blocks; each then leaves a partial (reference exponent, row
+// sum, unnormalised output) that `fold_partials_kernel` merges.
+struct WorkItem {
+  int sequence;        // index into the step's sequences
+  int row0;            // first token row of the tile in the step
+  int rows;            // <= 128
+  int pos0;            // position of the first row in its sequence
+  int first_key_tile;  // first key tile (of 64 keys) this block walks
+  int key_tiles;       // how many
+  int partial;         // -1: write the output; else the index of this block's partial
+  int reserved;
+};
+static_assert(sizeof(WorkItem) == 32, "eight ints");
+
 __global__ void __launch_bounds__(kThreads, 2)
 prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap q_map,
                             const __grid_constant__ CUtensorMap k_map,
                             const __grid_constant__ CUtensorMap v_map,
-                            __nv_bfloat16* __restrict__ out, const int4* __restrict__ q_tiles,
+                            __nv_bfloat16* __restrict__ out, const WorkItem* __restrict__ work,
+                            float* __restrict__ part_o, float* __restrict__ part_ml,
                             const int32_t* __restrict__ seq_lens,
                             const int32_t* __restrict__ block_table, int max_blocks, int heads,
                             int kv_heads, float scale_log2e, int window, int* __restrict__ error) {
@@ -92,16 +107,15 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap q_map,
 
   // blockIdx.x = head, blockIdx.y = tile: the tiles come heaviest first, so the blocks that
   // start first are the long ones of every head, and the short ones fill in behind them
-  const int4 tile = q_tiles[blockIdx.y];
-  const int b = tile.x, row0 = tile.y, rows = tile.z, pos0 = tile.w;
+  const WorkItem item = work[blockIdx.y];
+  const int b = item.sequence, row0 = item.row0, rows = item.rows, pos0 = item.pos0;
   const int h = blockIdx.x;
   const int g = h / (heads / kv_heads);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int kv_len = seq_lens[b];
   const int last_pos = pos0 + rows - 1;
-  const int first_key = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
-  const int t0 = first_key / KT;
-  const int n = last_pos / KT + 1 - t0;          // key tiles t0 .. t0 + n - 1
+  const int t0 = item.first_key_tile;
+  const int n = item.key_tiles;                  // key tiles t0 .. t0 + n - 1
 
   if (threadIdx.x == 0) {
     tma::mbar_init(&bar->q_full, 1);
@@ -292,8 +306,25 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap q_map,
     }
     if (ok && n > 0 && tma::mbar_wait(&bar->pv_done, (n - 1) & 1, error, 410)) {
       tc::fence_after_sync();
+      if (item.partial >= 0) {
+        // a share of the tile's keys: leave (m_ref, l, O) for the fold
+        const long long slot = ((long long)item.partial * heads + h) * QT + r;
+        part_ml[slot * 2] = m_ref;
+        part_ml[slot * 2 + 1] = l;
+        float* po = part_o + slot * D;
+#pragma unroll
+        for (int c = 0; c < D; c += 16) {
+          float v[16];
+          tc::ld_32x32b_x16(lane_base + kOCol + c, v);
+#pragma unroll
+          for (int i = 0; i < 16; i += 4)
+            *reinterpret_cast<float4*>(po + c + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+        }
+        l = 1.f;                // (nothing below is stored)
+      }
       const float inv = 1.f / l;
       __nv_bfloat16* dst = out + ((long long)(row0 + r) * heads + h) * D;
+      if (item.partial < 0)
 #pragma unroll
       for (int c = 0; c < D; c += 16) {
         float v[16];
@@ -316,6 +347,40 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap q_map,
   }
 }
 
+constexpr int kFoldRows = 8;      // rows (warps) per block of the fold
+
+// folds[i] = {first partial, count, first token row, rows}: out = sum_s O_s 2^(m_s - M) /
+// sum_s l_s 2^(m_s - M) for each row of the tile and each head (blockIdx.y).
+__global__ void fold_partials_kernel(const int4* __restrict__ folds, const float* __restrict__ part_o,
+                                     const float* __restrict__ part_ml,
+                                     __nv_bfloat16* __restrict__ out, int heads) {
+  const int4 f = folds[blockIdx.x / (QT / kFoldRows)];
+  const int h = blockIdx.y;
+  const int r = (blockIdx.x % (QT / kFoldRows)) * kFoldRows + (threadIdx.x >> 5);   // a warp per row
+  if (r < f.w) {
+    const int lane = threadIdx.x & 31;
+    float big = -INFINITY;
+    for (int s = 0; s < f.y; ++s)
+      big = fmaxf(big, part_ml[(((long long)(f.x + s) * heads + h) * QT + r) * 2]);
+    const float use = (big == -INFINITY) ? 0.f : big;
+    float total = 0.f;
+    float acc[D / 32];
+#pragma unroll
+    for (int i = 0; i < D / 32; ++i) acc[i] = 0.f;
+    for (int s = 0; s < f.y; ++s) {
+      const long long slot = ((long long)(f.x + s) * heads + h) * QT + r;
+      const float w = mma::exp2_fast(part_ml[slot * 2] - use);
+      total += w * part_ml[slot * 2 + 1];
+#pragma unroll
+      for (int i = 0; i < D / 32; ++i) acc[i] += w * part_o[slot * D + i * 32 + lane];
+    }
+    const float inv = 1.f / total;
+    __nv_bfloat16* dst = out + ((long long)(f.z + r) * heads + h) * D;
+#pragma unroll
+    for (int i = 0; i < D / 32; ++i) dst[i * 32 + lane] = __float2bfloat16_rn(acc[i] * inv);
+  }
+}
+
 __device__ int g_error;
 
 }  // namespace
@@ -329,14 +394,22 @@ SAKV_EXPORT int sakv_prefill_attention_tc_qmap(void* map, const void* qkv, long 
                                (uint64_t)width, (uint64_t)row_stride * 2, QT, 64);
 }
 
+// `work`: n_work items of 8 ints (see WorkItem); `folds`: n_folds items of 4 ints {first
+// partial, count, first token row, rows}; `part_o`, `part_ml`: scratch for the partials,
+// [partials, heads, 128, 128] and [partials, heads, 128, 2] floats (unused without folds).
 SAKV_EXPORT int sakv_prefill_attention_tc(const void* q_map, const void* k_map, const void* v_map,
                                           void* out, const int32_t* q_tiles, int n_tiles,
-                                          const int32_t* seq_lens, const int32_t* block_table,
+                                          const int32_t* folds, int n_folds, float* part_o,
+                                          float* part_ml, const int32_t* seq_lens,
+                                          const int32_t* block_table,
                                           int max_blocks, int heads, int kv_heads, int head_dim,
                                           float scale, int window, cudaStream_t stream) {
   if (n_tiles < 0 || n_tiles > 65535 || heads <= 0 || kv_heads <= 0 || heads % kv_heads ||
       max_blocks <= 0 || head_dim != D || (reinterpret_cast<uintptr_t>(q_tiles) & 15) ||
-      (reinterpret_cast<uintptr_t>(out) & 15))
+      (reinterpret_cast<uintptr_t>(out) & 15) || n_folds < 0 || n_folds > (1 << 20) ||
+      (n_folds > 0 && (!folds || !part_o || !part_ml ||
+                       (reinterpret_cast<uintptr_t>(folds) & 15) ||
+                       (reinterpret_cast<uintptr_t>(part_o) & 15))))
     return cudaErrorInvalidValue;
   if (n_tiles == 0) return 0;
   static bool configured = false;
@@ -355,9 +428,15 @@ SAKV_EXPORT int sakv_prefill_attention_tc(const void* q_map, const void* k_map, 
   }
   prefill_attention_tc_kernel<<<dim3(heads, n_tiles), kThreads, kSmemBytes, stream>>>(
       *(const CUtensorMap*)q_map, *(const CUtensorMap*)k_map, *(const CUtensorMap*)v_map,
-      (__nv_bfloat16*)out, (const int4*)q_tiles, seq_lens, block_table, max_blocks, heads,
-      kv_heads, scale * 1.4426950408889634f, window, error);
-  return launch_status();
+      (__nv_bfloat16*)out, (const WorkItem*)q_tiles, part_o, part_ml, seq_lens, block_table,
+      max_blocks, heads, kv_heads, scale * 1.4426950408889634f, window, error);
+  int status = launch_status();
+  if (status == 0 && n_folds > 0) {
+    fold_partials_kernel<<<dim3(n_folds * (QT / kFoldRows), heads), kFoldRows * 32, 0, stream>>>(
+        (const int4*)folds, part_o, part_ml, (__nv_bfloat16*)out, heads);
+    status = launch_status();
+  }
+  return status;
 }
 
 SAKV_EXPORT int sakv_prefill_attention_tc_error(int* value) {

@@ -19,7 +19,6 @@ import numpy as np
 import torch
 
 QUERY_TILE = 64       # tokens per query tile of the mma.sync prefill kernel; also the cache block
-WIDE_TILE = 128       # tokens per query tile of the tcgen05 prefill kernel
 
 
 @dataclass
@@ -44,7 +43,8 @@ class StepContext:
     is_decode: bool = False           # every sequence brings exactly one token
     max_len_bound: int = 0            # a bound on max_len that changes rarely (block-list width)
     q_tiles: torch.Tensor | None = None   # int32 [n, 4]: (sequence, first row, rows <= 64, first position)
-    q_tiles_wide: torch.Tensor | None = None   # the same in tiles of up to 128 rows
+    plans: dict = field(default_factory=dict)   # what a part worked out for this step, for its
+                                                # other layers to use again (key chosen by the part)
 
 
 class StepStager:
@@ -88,16 +88,9 @@ class StepStager:
             for a in range(0, c, QUERY_TILE):
                 tiles.append((i, row + a, min(QUERY_TILE, c - a), s + a))
             row += c
-        wide, row = [], 0
-        for i, (s, c) in enumerate(zip(starts, counts)):
-            for a in range(0, c, WIDE_TILE):
-                wide.append((i, row + a, min(WIDE_TILE, c - a), s + a))
-            row += c
-        for lst in (tiles, wide):
-            lst.sort(key=lambda t: -(t[3] + t[2]))   # the tiles with the most keys start first
+        tiles.sort(key=lambda t: -(t[3] + t[2]))     # the tiles with the most keys start first
         fields = [("token_ids", T), ("positions", T), ("token_seq", T), ("cu_seqlens", B + 1),
-                  ("seq_lens", B), ("slots", B), ("want", W), ("q_tiles", 4 * len(tiles)),
-                  ("q_tiles_wide", 4 * len(wide))]
+                  ("seq_lens", B), ("slots", B), ("want", W), ("q_tiles", 4 * len(tiles))]
         fields += [(f"table{g}", t.size) for g, t in enumerate(tables)]
         offsets, total = {}, 0
         for name, n in fields:
@@ -124,7 +117,6 @@ class StepStager:
         put("slots", slots)
         put("want", want_rows)
         put("q_tiles", np.asarray(tiles, dtype=np.int32))
-        put("q_tiles_wide", np.asarray(wide, dtype=np.int32))
         for g, t in enumerate(tables):
             put(f"table{g}", t)
         self.last_bytes = 4 * total
@@ -144,5 +136,4 @@ class StepStager:
             max_position=max(ends) - 1 if ends else 0, max_new=max(counts, default=0),
             max_len=max(ends, default=0), is_decode=all(c == 1 for c in counts),
             max_len_bound=min(width, max((t.shape[1] for t in tables), default=width)) * QUERY_TILE,
-            q_tiles=view("q_tiles", 4 * len(tiles)).view(len(tiles), 4),
-            q_tiles_wide=view("q_tiles_wide", 4 * len(wide)).view(len(wide), 4))
+            q_tiles=view("q_tiles", 4 * len(tiles)).view(len(tiles), 4))

@@ -15,10 +15,10 @@ from ._lib import (BF16, CACHE_BLOCK, F32, KernelError, call, dtype_code, plain_
 from .linear import gated_up, linear
 from . import gemm_tc
 from .attention import (attention_decode, attention_prefill, attention_prefill_tc, decode_splits,
-                        fast_path_takes, kernel_errors, tc_prefill_takes)
+                        fast_path_takes, kernel_errors, plan_wide_tiles, tc_prefill_takes, upload_wide_plan)
 
 __all__ = ["CACHE_BLOCK", "KernelError", "embed", "rms_norm", "rope_store", "attention_plain",
-           "attention_decode", "attention_prefill", "attention_prefill_tc", "tc_prefill_takes",
+           "attention_decode", "attention_prefill", "attention_prefill_tc", "tc_prefill_takes", "plan_wide_tiles", "upload_wide_plan",
            "decode_splits", "fast_path_takes",
            "kernel_errors", "gated_silu", "gated_up", "gemm_tc", "add_into", "linear", "choose"]
 

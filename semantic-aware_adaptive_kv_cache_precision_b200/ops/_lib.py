@@ -35,7 +35,7 @@ SIGNATURES = {
     "sakv_prefill_attention": ("attention_prefill",
                                [P, P, P, L, P, P, I, P, P, I, I, I, I, F, I, P]),
     "sakv_prefill_attention_tc": ("attention_prefill_tc",
-                                  [P, P, P, P, P, I, P, P, I, I, I, I, F, I, P]),
+                                  [P, P, P, P, P, I, P, I, P, P, P, P, I, I, I, I, F, I, P]),
     "sakv_gemm_tc": ("gemm_tc", [P, P, I, I, I, I, I, I, I, P, I, P, L, P]),
 }
 

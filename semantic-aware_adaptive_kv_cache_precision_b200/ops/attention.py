@@ -105,22 +105,71 @@ def tc_prefill_takes(dtype: torch.dtype, heads: int, kv_heads: int, head_dim: in
     return dtype == torch.bfloat16 and head_dim == 128 and heads % kv_heads == 0
 
 
+def plan_wide_tiles(starts, counts, heads: int, window=None, tile: int = 128,
+                    slots: int = 2 * SM_COUNT):
+    """Work items and folds of the tcgen05 prefill kernel for sequences that hold `starts[i]`
+    positions and bring `counts[i]` tokens. Each query tile of up to 128 tokens walks the key
+    tiles (64 keys) its rows can see. When all blocks of the step run at once (`slots` of
+    them fit the GPU), the longest tile decides its time, so the key tiles of the long ones
+    are dealt to several blocks that leave partials to be folded; with more blocks than that
+    the fold costs more than the balance gains (measured: 2,048 tokens 46 -> 38 us, 4,096
+    tokens 92 -> 98 us). Returns (work [n, 8], folds [m, 4], partials)."""
+    tiles, row = [], 0
+    for i, (s, c) in enumerate(zip(starts, counts)):
+        for a in range(0, c, tile):
+            rows, pos0 = min(tile, c - a), s + a
+            last = pos0 + rows - 1
+            first_key = max(0, pos0 - window + 1) if window else 0
+            t0 = first_key // CACHE_BLOCK
+            tiles.append((i, row + a, rows, pos0, t0, last // CACHE_BLOCK + 1 - t0))
+        row += c
+    steps = sum(t[5] for t in tiles) * heads
+    limit = None
+    if len(tiles) * heads < slots:                         # one wave: balance it
+        limit = max(8, -(-steps * 13 // (slots * 10)))
+    work, folds, partials = [], [], 0
+    for (i, r0, rows, pos0, t0, n) in tiles:
+        pieces = 1 if limit is None or n <= limit else -(-n // limit)
+        if pieces == 1:
+            work.append((i, r0, rows, pos0, t0, n, -1, 0))
+            continue
+        per = -(-n // pieces)
+        folds.append((partials, pieces, r0, rows))
+        for p in range(pieces):
+            work.append((i, r0, rows, pos0, t0 + p * per, min(per, n - p * per), partials, 0))
+            partials += 1
+    work.sort(key=lambda w: -w[5])                         # the longest blocks start first
+    return work, folds, partials
+
+
+def upload_wide_plan(starts, counts, heads: int, window, device, **how):
+    """`plan_wide_tiles` on the device: (work, folds or None, partials)."""
+    work, folds, partials = plan_wide_tiles(starts, counts, heads, window, **how)
+    flat = torch.tensor([x for w in work for x in w] + [x for f in folds for x in f],
+                        dtype=torch.int32).pin_memory().to(device, non_blocking=True)
+    n = 8 * len(work)
+    return (flat[:n].view(-1, 8), flat[n:].view(-1, 4) if folds else None, partials)
+
+
+_wide_scratch: dict = {}
+
+
 def attention_prefill_tc(qkv: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
-                         q_tiles: torch.Tensor, seq_lens: torch.Tensor, block_table: torch.Tensor,
-                         heads: int, kv_heads: int, head_dim: int, scale: float,
-                         window) -> torch.Tensor:
-    """The tcgen05 prefill kernel. `q_tiles`: int32 [n, 4] = (sequence, first token row,
-    rows <= 128, first position)."""
-    require_cuda(qkv, k_cache, v_cache, q_tiles, seq_lens, block_table)
+                         work: torch.Tensor, folds, partials: int, seq_lens: torch.Tensor,
+                         block_table: torch.Tensor, heads: int, kv_heads: int, head_dim: int,
+                         scale: float, window) -> torch.Tensor:
+    """The tcgen05 prefill kernel. `work` (int32 [n, 8]), `folds` (int32 [m, 4] or None) and
+    `partials` come from `plan_wide_tiles`, on the device."""
+    require_cuda(qkv, k_cache, v_cache, work, seq_lens, block_table)
     if not tc_prefill_takes(qkv.dtype, heads, kv_heads, head_dim):
         raise KernelError("attention_prefill_tc: sizes not taken (bf16, head_dim 128)")
     if qkv.stride(1) != 1 or qkv.shape[1] < heads * head_dim or (qkv.stride(0) % 8) \
             or qkv.data_ptr() % 16:
         raise KernelError("attention_prefill_tc: qkv must be [T, >= heads * head_dim] with rows "
                           "a multiple of 16 bytes apart")
-    if q_tiles.dtype != torch.int32 or q_tiles.dim() != 2 or q_tiles.shape[1] != 4 \
-            or not q_tiles.is_contiguous():
-        raise KernelError("attention_prefill_tc: q_tiles must be int32 [n, 4]")
+    if work.dtype != torch.int32 or work.dim() != 2 or work.shape[1] != 8 \
+            or not work.is_contiguous():
+        raise KernelError("attention_prefill_tc: work must be int32 [n, 8]")
     raw = ctypes.create_string_buffer(128 + 64)
     q_map = (ctypes.addressof(raw) + 63) & ~63
     code = plain_function("sakv_prefill_attention_tc_qmap")(q_map, qkv.data_ptr(), qkv.shape[0],
@@ -128,9 +177,20 @@ def attention_prefill_tc(qkv: torch.Tensor, k_cache: torch.Tensor, v_cache: torc
     if code != 0:
         raise KernelError(f"could not make a TMA descriptor for the queries (error {code})")
     out = torch.empty((qkv.shape[0], heads * head_dim), dtype=torch.bfloat16, device=qkv.device)
+    part_o = part_ml = None
+    n_folds = 0 if folds is None else folds.shape[0]
+    if n_folds:
+        need = partials * heads * 128 * (head_dim + 2)
+        scratch = _wide_scratch.get(qkv.device)
+        if scratch is None or scratch.numel() < need:
+            scratch = torch.empty(max(need, 1 << 22), dtype=torch.float32, device=qkv.device)
+            _wide_scratch[qkv.device] = scratch
+        part_o = scratch[:partials * heads * 128 * head_dim]
+        part_ml = scratch[partials * heads * 128 * head_dim:need]
     call("sakv_prefill_attention_tc", q_map, tensor_map(k_cache), tensor_map(v_cache), ptr(out),
-         ptr(q_tiles), q_tiles.shape[0], ptr(seq_lens), ptr(block_table), block_table.shape[1],
-         heads, kv_heads, head_dim, float(scale), int(window) if window else 0)
+         ptr(work), work.shape[0], ptr(folds) if n_folds else None, n_folds, ptr(part_o),
+         ptr(part_ml), ptr(seq_lens), ptr(block_table), block_table.shape[1], heads, kv_heads,
+         head_dim, float(scale), int(window) if window else 0)
     return out
 
 

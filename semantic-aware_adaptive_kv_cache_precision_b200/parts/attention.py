@@ -95,9 +95,13 @@ class GQAAttention(Part):
                 return ops.attention_decode(qkv, view.keys, view.values, step.seq_lens,
                                             view.block_table, s.heads, s.kv_heads, s.head_dim,
                                             s.scale, s.window, step.max_len_bound or step.max_len)
-            if ops.tc_prefill_takes(qkv.dtype, s.heads, s.kv_heads, s.head_dim) \
-                    and step.q_tiles_wide is not None:
-                return ops.attention_prefill_tc(qkv, view.keys, view.values, step.q_tiles_wide,
+            if ops.tc_prefill_takes(qkv.dtype, s.heads, s.kv_heads, s.head_dim) and step.starts:
+                key = ("wide_tiles", s.heads, s.window)
+                plan = step.plans.get(key)
+                if plan is None:       # the same for every layer of these sizes: made once a step
+                    plan = step.plans[key] = ops.upload_wide_plan(
+                        step.starts, step.new_counts, s.heads, s.window, qkv.device)
+                return ops.attention_prefill_tc(qkv, view.keys, view.values, *plan,
                                                 step.seq_lens, view.block_table, s.heads,
                                                 s.kv_heads, s.head_dim, s.scale, s.window)
             return ops.attention_prefill(qkv, view.keys, view.values, step.q_tiles,

@@ -544,24 +544,26 @@ def test_vector_paths_of_the_elementwise_kernels(dtype):
     np.testing.assert_allclose(host(acc), want, rtol=0, atol=1e-6)
 
 
-@pytest.mark.parametrize("heads,kv_heads,window", [(12, 2, None), (4, 4, None), (7, 1, 200),
-                                                   (6, 3, 64)])
-def test_attention_prefill_tcgen05_kernel(heads, kv_heads, window):
+# slots: how many blocks the plan believes run at once; 1 deals no tile to several blocks,
+# a huge number cuts every tile of more than 8 key tiles
+@pytest.mark.parametrize("heads,kv_heads,window,slots", [
+    (12, 2, None, 296), (4, 4, None, 1), (4, 4, None, 10 ** 6), (7, 1, 200, 10 ** 6),
+    (6, 3, 64, 296), (2, 1, 700, 10 ** 6)])
+def test_attention_prefill_tcgen05_kernel(heads, kv_heads, window, slots):
     d = 128
     rng = np.random.default_rng(heads + (window or 0))
-    cases = [(0, 150), (0, 128), (299, 1), (64, 2), (100, 130), (0, 1), (37, 91), (600, 300)]
+    cases = [(0, 150), (0, 128), (299, 1), (64, 2), (100, 130), (0, 1), (37, 91), (600, 300),
+             (0, 1100)]
     lengths = [a + n for a, n in cases]
     k_cache, v_cache, table = paged_case(rng, lengths, kv_heads, d)
     T = sum(n for _, n in cases)
     width = (heads + 2 * kv_heads) * d
     qkv = dev(rng.standard_normal((T, width)), torch.bfloat16)
-    tiles, row = [], 0
-    for i, (a, n) in enumerate(cases):
-        for s in range(0, n, 128):
-            tiles.append((i, row + s, min(128, n - s), a + s))
-        row += n
+    plan = ops.upload_wide_plan([a for a, _ in cases], [n for _, n in cases], heads, window,
+                                "cuda", slots=slots)
+    assert slots > 1 or plan[1] is None
     scale = d ** -0.5
-    got = ops.attention_prefill_tc(qkv, k_cache, v_cache, dev(tiles, torch.int32),
+    got = ops.attention_prefill_tc(qkv, k_cache, v_cache, *plan,
                                    dev(lengths, torch.int32), dev(table, torch.int32), heads,
                                    kv_heads, d, scale, window)
     assert ops.kernel_errors()["sakv_prefill_attention_tc_error"] == 0
