@@ -5,6 +5,10 @@
 // given, picks which input row each output row normalises (used to take only
 // the positions whose logits are wanted). The order of the additions depends on
 // the row length alone, never on how many rows are in the batch.
+//
+// With `add` (fp32, same shape as x) the kernel first folds it into the stream,
+// x += add, stores x and normalises the sum: the residual add of the layer before
+// and this norm read and write the stream once instead of twice.
 #include "common.cuh"
 
 namespace {
@@ -15,10 +19,11 @@ namespace {
 constexpr int kThreads = 256;
 constexpr int kPerThread = 4;          // float4 loads per thread: rows up to 4096 wide
 
-template <typename W, typename Out>
+template <typename W, typename Out, bool kAdd = false>
 __global__ void __launch_bounds__(kThreads)
-rmsnorm_kernel(const float* __restrict__ x, const int32_t* __restrict__ rows,
-               const W* __restrict__ weight, Out* __restrict__ out, int hidden, float eps) {
+rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ add,
+               const int32_t* __restrict__ rows, const W* __restrict__ weight,
+               Out* __restrict__ out, int hidden, float eps) {
   __shared__ float scratch[33];
   let_next_kernel_start();
   const bool fits = hidden <= kThreads * 4 * kPerThread && (hidden & 3) == 0;
@@ -35,7 +40,8 @@ rmsnorm_kernel(const float* __restrict__ x, const int32_t* __restrict__ rows,
   }
   wait_for_previous_kernel();
   const long long src = rows ? rows[blockIdx.x] : blockIdx.x;
-  const float* in = x + src * hidden;
+  float* in = x + src * hidden;
+  const float* more = kAdd ? add + src * hidden : nullptr;
   Out* o = out + (long long)blockIdx.x * hidden;
   if (fits) {
     float4 v[kPerThread];
@@ -44,6 +50,14 @@ rmsnorm_kernel(const float* __restrict__ x, const int32_t* __restrict__ rows,
     for (int i = 0; i < kPerThread; ++i) {
       const int c = (i * kThreads + threadIdx.x) * 4;
       v[i] = c < hidden ? *reinterpret_cast<const float4*>(in + c) : make_float4(0, 0, 0, 0);
+      if (kAdd && c < hidden) {
+        const float4 a = *reinterpret_cast<const float4*>(more + c);
+        v[i].x += a.x;
+        v[i].y += a.y;
+        v[i].z += a.z;
+        v[i].w += a.w;
+        *reinterpret_cast<float4*>(in + c) = v[i];
+      }
       acc += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
     }
     const float scale = rsqrtf(block_sum(acc, scratch) / static_cast<float>(hidden) + eps);
@@ -61,7 +75,8 @@ rmsnorm_kernel(const float* __restrict__ x, const int32_t* __restrict__ rows,
   }
   float acc = 0.f;
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
-    const float v = in[i];
+    float v = in[i];
+    if (kAdd) in[i] = v = v + more[i];   // (read again below by this thread)
     acc += v * v;
   }
   const float scale = rsqrtf(block_sum(acc, scratch) / static_cast<float>(hidden) + eps);
@@ -71,15 +86,26 @@ rmsnorm_kernel(const float* __restrict__ x, const int32_t* __restrict__ rows,
 
 }  // namespace
 
-SAKV_EXPORT int sakv_rmsnorm(const float* x, const int32_t* rows, const void* weight,
+// `add`: null, or fp32 [n_rows, hidden] that is folded into x first (then `rows` must be
+// null, and the weight and the output bf16).
+SAKV_EXPORT int sakv_rmsnorm(float* x, const float* add, const int32_t* rows, const void* weight,
                              int weight_dtype, void* out, int out_dtype, int n_rows, int hidden,
                              float eps, cudaStream_t stream) {
-  if (n_rows < 0 || hidden <= 0) return cudaErrorInvalidValue;
+  if (n_rows < 0 || hidden <= 0 || (add && rows)) return cudaErrorInvalidValue;
   if (n_rows == 0) return 0;
   const int threads = kThreads;
+  if (add) {
+    if ((reinterpret_cast<uintptr_t>(add) & 15) || weight_dtype != SAKV_BF16 ||
+        out_dtype != SAKV_BF16)
+      return cudaErrorInvalidValue;
+    return launch_overlapped(rmsnorm_kernel<__nv_bfloat16, __nv_bfloat16, true>, dim3(n_rows),
+                             dim3(threads), 0, stream, 1, x, add, rows,
+                             (const __nv_bfloat16*)weight, (__nv_bfloat16*)out, hidden, eps);
+  }
 #define LAUNCH(W, O)                                                                          \
   return launch_overlapped(rmsnorm_kernel<W, O>, dim3(n_rows), dim3(threads), 0, stream, 1, x, \
-                           rows, (const W*)weight, (O*)out, hidden, eps)
+                           (const float*)nullptr, rows, (const W*)weight, (O*)out,     \
+                           hidden, eps)
   if (weight_dtype == SAKV_F32 && out_dtype == SAKV_F32) LAUNCH(float, float);
   if (weight_dtype == SAKV_F32 && out_dtype == SAKV_BF16) LAUNCH(float, __nv_bfloat16);
   if (weight_dtype == SAKV_BF16 && out_dtype == SAKV_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);

@@ -89,10 +89,20 @@ class DecoderModel:
             raise RuntimeError("no weights on the device; load a checkpoint first")
         x = ops.embed(step.token_ids, self.embed)
         written = set()
+        pending = None          # a block's last output, not yet added to the stream
         for call in self.spec.run_order:
             view = cache.entry_view(call.cache, step.tables)
-            self.blocks[call.block].forward(x, step, view, call.cache not in written)
+            block = self.blocks[call.block]
+            if getattr(block, "carries_pending", False):
+                pending = block.forward(x, step, view, call.cache not in written, pending)
+            else:
+                if pending is not None:
+                    ops.add_into(x, pending)
+                block.forward(x, step, view, call.cache not in written)
+                pending = None
             written.add(call.cache)
+        if pending is not None:
+            ops.add_into(x, pending)
         return x
 
     def logits(self, x: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:

@@ -12,7 +12,7 @@ import torch
 
 from ._lib import (BF16, CACHE_BLOCK, F32, KernelError, call, dtype_code, plain_function, ptr,
                    require_cuda)
-from .linear import gated_up, linear
+from .linear import Deferred, gated_up, linear
 from . import gemm_tc
 from .attention import (attention_decode, attention_prefill, attention_prefill_tc, decode_splits,
                         fast_path_takes, kernel_errors, plan_wide_tiles, tc_prefill_takes, upload_wide_plan)
@@ -20,7 +20,7 @@ from .attention import (attention_decode, attention_prefill, attention_prefill_t
 __all__ = ["CACHE_BLOCK", "KernelError", "embed", "rms_norm", "rope_store", "attention_plain",
            "attention_decode", "attention_prefill", "attention_prefill_tc", "tc_prefill_takes", "plan_wide_tiles", "upload_wide_plan",
            "decode_splits", "fast_path_takes",
-           "kernel_errors", "gated_silu", "gated_up", "gemm_tc", "add_into", "linear", "choose"]
+           "kernel_errors", "gated_silu", "gated_up", "gemm_tc", "add_into", "linear", "choose", "prefetch_l2", "Deferred"]
 
 
 def _check(cond: bool, message: str) -> None:
@@ -44,9 +44,11 @@ def embed(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor | None = Non
 
 
 def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch.dtype,
-             rows: torch.Tensor | None = None) -> torch.Tensor:
-    """RMSNorm of rows of fp32 `x`; with `rows` (int32), of those rows only."""
-    require_cuda(x, weight, rows)
+             rows: torch.Tensor | None = None, add: torch.Tensor | None = None) -> torch.Tensor:
+    """RMSNorm of rows of fp32 `x`; with `rows` (int32), of those rows only. With `add`
+    (fp32, x's shape; bf16 weight and output) `x += add` happens first, in the same kernel,
+    and x keeps the sum."""
+    require_cuda(x, weight, rows, add)
     _check(x.dtype == torch.float32 and x.dim() == 2 and x.is_contiguous(), "x: fp32 [T, hidden]")
     hidden = x.shape[1]
     _check(weight.shape == (hidden,) and weight.is_contiguous(), "weight: [hidden]")
@@ -55,10 +57,24 @@ def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch
         _check(rows.dtype == torch.int32 and rows.dim() == 1 and rows.is_contiguous(),
                "rows: int32 [R]")
         n = rows.numel()
+    if add is not None:
+        _check(rows is None and add.dtype == torch.float32 and add.shape == x.shape
+               and add.is_contiguous() and weight.dtype == torch.bfloat16
+               and out_dtype == torch.bfloat16, "add: fp32 like x, bf16 weight and output, no rows")
     out = torch.empty((n, hidden), dtype=out_dtype, device=x.device)
-    call("sakv_rmsnorm", ptr(x), ptr(rows), ptr(weight), dtype_code(weight.dtype), ptr(out),
+    call("sakv_rmsnorm", ptr(x), ptr(add), ptr(rows), ptr(weight), dtype_code(weight.dtype), ptr(out),
          dtype_code(out_dtype), n, hidden, float(eps))
     return out
+
+
+def prefetch_l2(t: torch.Tensor) -> None:
+    """Ask the L2 cache for a tensor's bytes (weights that a kernel a few launches on will
+    stream); returns at once and runs beside the kernel before it."""
+    require_cuda(t)
+    size = t.numel() * t.element_size()
+    if not t.is_contiguous() or t.data_ptr() % 16 or size % 16:
+        return
+    call("sakv_prefetch_l2", ptr(t), size)
 
 
 def rope_store(qkv: torch.Tensor, positions: torch.Tensor, token_seq: torch.Tensor,

@@ -24,7 +24,8 @@ SIGNATURES = {
     "sakv_embed": ("elementwise", [P, P, I, P, I, I, I, P]),
     "sakv_gated_silu": ("elementwise", [P, P, I, I, I, P]),
     "sakv_add_into": ("elementwise", [P, P, I, L, P]),
-    "sakv_rmsnorm": ("norm", [P, P, P, I, P, I, I, I, F, P]),
+    "sakv_prefetch_l2": ("elementwise", [P, L, P]),
+    "sakv_rmsnorm": ("norm", [P, P, P, P, I, P, I, I, I, F, P]),
     "sakv_rope_store": ("rope", [P, I, L, P, P, P, I, P, P, I, P, P, I, I, I, I, I, P]),
     "sakv_attention_plain": ("attention_plain",
                              [P, I, L, P, P, P, P, P, P, I, I, I, I, I, F, I, P]),

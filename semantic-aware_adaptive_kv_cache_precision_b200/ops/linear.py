@@ -25,6 +25,15 @@ from ._lib import KernelError, call, ptr, require_cuda
 TC_MAX_TOKENS = 64
 
 
+class Deferred:
+    """An fp32 product that its caller still has to add to the accumulator it named."""
+
+    __slots__ = ("delta",)
+
+    def __init__(self, delta: torch.Tensor):
+        self.delta = delta
+
+
 def gated_up(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
     """`silu(x Wgate^T) * (x Wup^T)` for `w_gate_up = [Wgate; Wup]`: one kernel with the
     activation in its epilogue where the tensor-core kernel takes the operands, else the
@@ -39,11 +48,16 @@ def gated_up(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
 
 def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None, *,
            out_dtype: torch.dtype | None = None,
-           accumulate_into: torch.Tensor | None = None) -> torch.Tensor:
+           accumulate_into: torch.Tensor | None = None, may_defer: bool = False):
     """`x`: [T, K]; `weight`: [N, K] as stored in the checkpoint; `bias`: [N] or None.
 
     With `accumulate_into` (fp32 [T, N]) the product is added to it in fp32 and it
     is returned; otherwise a new [T, N] tensor of `out_dtype` (default: x's type).
+
+    With `may_defer` as well, a product that the library computed into a tensor of its own
+    is not added: the call returns `Deferred(delta)` with the fp32 product, and the caller
+    owes `accumulate_into += delta` (the norm that reads the sum next can do it on its way,
+    `rms_norm(..., add=delta)`). Kernels that add in their epilogue return the accumulator.
     """
     require_cuda(x, weight, bias, accumulate_into)
     if x.dim() != 2 or weight.dim() != 2 or x.shape[1] != weight.shape[1]:
@@ -88,6 +102,8 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = No
         y = torch.mm(xb, weight.t(), out_dtype=torch.float32)
         if bias is not None:
             y += bias.float()
+        if may_defer and acc.is_contiguous():
+            return Deferred(y)
         add_into(acc, y)
         return acc
     if out_dtype == torch.float32:

@@ -76,12 +76,15 @@ class GQAAttention(Part):
 
     # -- the step ---------------------------------------------------------------
 
-    def forward(self, h, step, view, residual, write_cache=True):
+    can_defer = True
+
+    def forward(self, h, step, view, residual, write_cache=True, defer=False):
         s = self.spec
         qkv = ops.linear(h, self.w_qkv, self.b_qkv, out_dtype=self.act_dtype)
         self.position.rotate_store(qkv, step, view, s.heads, s.kv_heads, s.head_dim, write_cache)
         attended = self.attend(qkv, step, view)
-        ops.linear(attended, self.w_o, self.b_o, accumulate_into=residual)
+        out = ops.linear(attended, self.w_o, self.b_o, accumulate_into=residual, may_defer=defer)
+        return out.delta if isinstance(out, ops.Deferred) else None
 
     def attend(self, qkv, step, view):
         """Tensor-core kernels where they take the sizes (bf16, head_dim 64 or 128, up

@@ -4,6 +4,7 @@ with the residual stream `x` in fp32 from the embedding to the final norm
 
 from __future__ import annotations
 
+from .. import ops
 from .base import Part, build_part, register_part
 
 
@@ -32,9 +33,34 @@ class PreNormBlock(Part):
     def cache_need(self):
         return self.mixer.cache_need()
 
-    def forward(self, x, step, view, write_cache=True):
-        self.mixer.forward(self.mixer_norm.forward(x), step, view, x, write_cache)
-        self.ffn.forward(self.ffn_norm.forward(x), step, x)
+    # A mixer or feed-forward with `can_defer` may hand back its fp32 output instead of adding
+    # it to the stream (`defer=True`); the norm that reads the stream next adds it on its way
+    # if it has `folds_add`, so the stream is read and written once instead of twice. What the
+    # feed-forward hands back leaves the block as `pending`: whoever runs the blocks gives it
+    # to the next one, or adds it to the stream at the end.
+    carries_pending = True
+
+    def forward(self, x, step, view, write_cache=True, pending=None):
+        h = _normed(self.mixer_norm, x, pending)
+        if getattr(self.mixer, "can_defer", False):
+            pending = self.mixer.forward(h, step, view, x, write_cache, defer=True)
+        else:
+            self.mixer.forward(h, step, view, x, write_cache)
+            pending = None
+        h = _normed(self.ffn_norm, x, pending)
+        if getattr(self.ffn, "can_defer", False):
+            return self.ffn.forward(h, step, x, defer=True)
+        self.ffn.forward(h, step, x)
+        return None
+
+
+def _normed(norm, x, pending):
+    if pending is None:
+        return norm.forward(x)
+    if getattr(norm, "folds_add", False):
+        return norm.forward(x, add=pending)
+    ops.add_into(x, pending)
+    return norm.forward(x)
 
 
 register_part("pre_norm", PreNormBlock)

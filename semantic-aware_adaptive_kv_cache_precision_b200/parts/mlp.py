@@ -34,9 +34,12 @@ class GatedMLP(Part):
                                         arena.view(p + "up_proj.weight")])
         self.w_down = arena.view(p + "down_proj.weight")
 
-    def forward(self, h, step, residual):
+    can_defer = True
+
+    def forward(self, h, step, residual, defer=False):
         act = ops.gated_up(h, self.w_gate_up)
-        ops.linear(act, self.w_down, accumulate_into=residual)
+        out = ops.linear(act, self.w_down, accumulate_into=residual, may_defer=defer)
+        return out.delta if isinstance(out, ops.Deferred) else None
 
 
 register_part("gated_mlp", GatedMLP)
