@@ -79,33 +79,7 @@ __global__ void add_into_kernel(float* __restrict__ acc, const T* __restrict__ y
     acc[i] += widen(y[i]);
 }
 
-// Asks the L2 cache to fetch [p, p + bytes) in pieces of `kPiece` bytes, one instruction a
-// piece, and returns without waiting for the data. It reads nothing a kernel before it wrote,
-// so it runs beside that kernel; it still waits for it before it ends, so that the kernel
-// after this one, which waits only for this one, is ordered behind both.
-constexpr int kPiece = 16384;
-__global__ void prefetch_l2_kernel(const char* __restrict__ p, long long bytes) {
-  let_next_kernel_start();
-  const long long pieces = (bytes + kPiece - 1) / kPiece;
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < pieces;
-       i += (long long)gridDim.x * blockDim.x) {
-    const long long at = i * kPiece;
-    const unsigned size = static_cast<unsigned>(bytes - at < kPiece ? bytes - at : kPiece);
-    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p + at), "r"(size) : "memory");
-  }
-  wait_for_previous_kernel();
-}
-
 }  // namespace
-
-// `p` 16-byte aligned, `bytes` a multiple of 16.
-SAKV_EXPORT int sakv_prefetch_l2(const void* p, long long bytes, cudaStream_t stream) {
-  if (bytes < 0 || (reinterpret_cast<uintptr_t>(p) & 15) || (bytes & 15)) return cudaErrorInvalidValue;
-  if (bytes == 0) return 0;
-  const long long pieces = (bytes + kPiece - 1) / kPiece;
-  return launch_overlapped(prefetch_l2_kernel, dim3(grid_for(pieces, 32, 148)), dim3(32), 0, stream,
-                           1, (const char*)p, bytes);
-}
 
 SAKV_EXPORT int sakv_embed(const int32_t* ids, const void* table, int table_dtype, float* out,
                            int tokens, int hidden, int vocab, cudaStream_t stream) {

@@ -41,6 +41,8 @@ enum : int { EPI_BF16 = 0, EPI_F32 = 1, EPI_ACCUM = 2, EPI_GATED = 3 };
 struct Params {
   int M, N, K;
   int splits, kb_per_split;
+  int parts;             // independent K ranges, each leaving a sum of its own (EPI_F32 only)
+  long long part_stride; // elements from one part's [M, ldo] result to the next
   int stages;            // tiles in flight per block (ring of shared-memory stages)
   int dual_offset;       // row of W where the "up" half starts (gated_silu)
   int epi;
@@ -97,10 +99,10 @@ __device__ __forceinline__ float bias_at(const Params& p, int n) {
                                   : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.bias)[n]);
 }
 
-__device__ __forceinline__ void finish(const Params& p, int m, int n, float c, float up,
+__device__ __forceinline__ void finish(const Params& p, int part, int m, int n, float c, float up,
                                        float bias) {
   if (m >= p.M || n >= p.N) return;
-  const long long at = (long long)m * p.ldo + n;
+  const long long at = (long long)m * p.ldo + n + part * p.part_stride;
   if (p.epi == EPI_BF16) {
     reinterpret_cast<__nv_bfloat16*>(p.out)[at] = __float2bfloat16_rn(c + bias);
   } else if (p.epi == EPI_F32) {
@@ -112,6 +114,49 @@ __device__ __forceinline__ void finish(const Params& p, int m, int n, float c, f
   } else {
     const float silu = c / (1.0f + expf(-c));
     reinterpret_cast<__nv_bfloat16*>(p.out)[at] = __float2bfloat16_rn(silu * up);
+  }
+}
+
+// The reduction of a cluster's partial tiles: this block finishes token columns `split`,
+// `split + S`, ... of its 128 rows by reading every block's partial through distributed
+// shared memory, four columns' worth of remote reads in flight at a time (measured in the
+// decode step: 2, 8 and 16 columns at a time are all slower). The usual cluster sizes (S =
+// 2, 4, 8) are compiled apart, so that the loops over the cluster unroll to its real size
+// (the decode step at 8 sequences: 1.68 -> 1.61 ms); S = 0 is any other size.
+template <int MT, bool kDual, int S>
+__device__ __forceinline__ void reduce_columns(const Params& p, uint32_t base, int split,
+                                               int k_part, int m0, int n, int row, float bias) {
+  constexpr int kS = S > 0 ? S : kMaxSplits;
+  constexpr int kBatch = 4;
+  const int splits = S > 0 ? S : p.splits;
+  for (int c0 = split; c0 < MT && m0 + c0 < p.M; c0 += kBatch * splits) {
+    float part[kBatch][kS], part_up[kDual ? kBatch : 1][kS];
+#pragma unroll
+    for (int j = 0; j < kBatch; ++j) {
+      const int c = c0 + j * splits;
+      const bool live = c < MT && m0 + c < p.M;
+#pragma unroll
+      for (int s = 0; s < kS; ++s) {
+        part[j][s] = 0.f;
+        if (kDual) part_up[j][s] = 0.f;
+        if (live && s < splits) {
+          part[j][s] = ld_peer(base + (c * BM + row) * 4, s);
+          if (kDual) part_up[j][s] = ld_peer(base + ((MT + c) * BM + row) * 4, s);
+        }
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < kBatch; ++j) {
+      const int c = c0 + j * splits;
+      if (c >= MT) break;
+      float acc = 0.f, up = 0.f;
+#pragma unroll
+      for (int s = 0; s < kS; ++s) {
+        acc += part[j][s];
+        if (kDual) up += part_up[j][s];
+      }
+      finish(p, k_part, m0 + c, n, acc, up, bias);
+    }
   }
 }
 
@@ -130,10 +175,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n_tile = blockIdx.x, m_tile = blockIdx.y, split = blockIdx.z;
+  // blockIdx.z = part * splits + split: a cluster is the `splits` blocks of one part
+  const int n_tile = blockIdx.x, m_tile = blockIdx.y;
+  const int split = blockIdx.z % p.splits, k_part = blockIdx.z / p.splits;
   const int n0 = n_tile * BM, m0 = m_tile * MT;
   const int total_kb = (p.K + BK - 1) / BK;
-  const int kb0 = split * p.kb_per_split;
+  const int kb0 = blockIdx.z * p.kb_per_split;
   const int kb1 = min(total_kb, kb0 + p.kb_per_split);
   const int n_kb = kb1 - kb0;
 
@@ -213,7 +260,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;          // lane of tensor memory = weight row in the tile
     const int n = n0 + row;
-    const float bias = bias_at(p, n);
+    const float bias = k_part == 0 ? bias_at(p, n) : 0.f;
     wait_for_previous_kernel();       // before any write to global memory
     const bool ok = tma::mbar_wait(accum, 0, p.error, 303);
     tc::fence_after_sync();
@@ -226,7 +273,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
           tc::ld_32x32b_x16(taddr + c, v);
           if (kDual) tc::ld_32x32b_x16(taddr + MT + c, u);
 #pragma unroll
-          for (int j = 0; j < 16; ++j) finish(p, m0 + c + j, n, v[j], kDual ? u[j] : 0.f, bias);
+          for (int j = 0; j < 16; ++j)
+            finish(p, k_part, m0 + c + j, n, v[j], kDual ? u[j] : 0.f, bias);
         }
       }
     } else if (ok) {
@@ -248,39 +296,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
     if (warp >= 2) {
       const int row = (warp & 3) * 32 + lane;
       const int n = n0 + row;
-      const float bias = bias_at(p, n);
+      const float bias = k_part == 0 ? bias_at(p, n) : 0.f;
       const uint32_t base = tma::smem_u32(smem);
-      // token columns split, split + splits, ... are finished by this block, four at a
-      // time so that all their partials are in flight together
-      constexpr int kBatch = 4;
-      for (int c0 = split; c0 < MT && m0 + c0 < p.M; c0 += kBatch * p.splits) {
-        float part[kBatch][kMaxSplits], part_up[kBatch][kMaxSplits];
-#pragma unroll
-        for (int j = 0; j < kBatch; ++j) {
-          const int c = c0 + j * p.splits;
-          const bool live = c < MT && m0 + c < p.M;
-#pragma unroll
-          for (int s = 0; s < kMaxSplits; ++s) {
-            part[j][s] = part_up[j][s] = 0.f;
-            if (live && s < p.splits) {
-              part[j][s] = ld_peer(base + (c * BM + row) * 4, s);
-              if (kDual) part_up[j][s] = ld_peer(base + ((MT + c) * BM + row) * 4, s);
-            }
-          }
-        }
-#pragma unroll
-        for (int j = 0; j < kBatch; ++j) {
-          const int c = c0 + j * p.splits;
-          if (c >= MT) break;
-          float acc = 0.f, up = 0.f;
-#pragma unroll
-          for (int s = 0; s < kMaxSplits; ++s) {
-            acc += part[j][s];
-            up += part_up[j][s];
-          }
-          finish(p, m0 + c, n, acc, up, bias);
-        }
-      }
+      // token columns split, split + splits, ... are finished by this block
+      if (p.splits == 2)
+        reduce_columns<MT, kDual, 2>(p, base, split, k_part, m0, n, row, bias);
+      else if (p.splits == 4)
+        reduce_columns<MT, kDual, 4>(p, base, split, k_part, m0, n, row, bias);
+      else if (p.splits == 8)
+        reduce_columns<MT, kDual, 8>(p, base, split, k_part, m0, n, row, bias);
+      else
+        reduce_columns<MT, kDual, 0>(p, base, split, k_part, m0, n, row, bias);
     }
     cluster_sync_all();       // nobody leaves while a peer may still read its shared memory
   }
@@ -306,11 +332,11 @@ int launch(const CUtensorMap* w_map, const CUtensorMap* x_map, Params p, int n_t
     if (e != cudaSuccess) return static_cast<int>(e);
     configured = true;
   }
-  p.stages = C::stages_for((long long)n_tiles * m_tiles * p.splits);
+  p.stages = C::stages_for((long long)n_tiles * m_tiles * p.splits * p.parts);
   while (C::smem_bytes(p.stages) > 227 * 1024) --p.stages;
   if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p.error), g_error) != cudaSuccess)
     return cudaErrorInvalidValue;
-  return launch_overlapped(gemm_tc_kernel<MT, kDual>, dim3(n_tiles, m_tiles, p.splits),
+  return launch_overlapped(gemm_tc_kernel<MT, kDual>, dim3(n_tiles, m_tiles, p.splits * p.parts),
                            dim3(kThreads), (size_t)C::smem_bytes(p.stages), stream, p.splits,
                            *w_map, *x_map, p);
 }
@@ -328,19 +354,32 @@ SAKV_EXPORT int sakv_gemm_tc_map(void* map, const void* base, long long rows, lo
                                (uint64_t)cols, (uint64_t)row_stride_elems * 2, box_rows, BK);
 }
 
+// `parts` > 1 (EPI_F32 only): K is cut into `parts` ranges whose sums are left apart, part i
+// at `out + i * part_stride`, for the reader to add; each range is split over a cluster of
+// `splits` as before. parts * splits must leave no K range empty (see sakv_gemm_tc_splits).
 SAKV_EXPORT int sakv_gemm_tc(const void* w_map, const void* x_map, int M, int N, int K, int mt,
-                             int splits, int epi, int dual_offset, const void* bias,
-                             int bias_dtype, void* out, long long ldo, cudaStream_t stream) {
+                             int splits, int parts, int epi, int dual_offset, const void* bias,
+                             int bias_dtype, void* out, long long ldo, long long part_stride,
+                             cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0 || (K % 8) || splits < 1 || epi < 0 || epi > EPI_GATED ||
-      ldo < N)
+      ldo < N || parts < 1 || parts > 64 || (parts > 1 && epi != EPI_F32))
     return cudaErrorInvalidValue;
   const int total_kb = (K + BK - 1) / BK;
-  if (splits > total_kb) splits = total_kb;
   if (splits > kMaxSplits) splits = kMaxSplits;
+  if (splits * parts > total_kb) {
+    if (parts > 1) return cudaErrorInvalidValue;
+    splits = total_kb;
+  }
   Params p;
   p.M = M; p.N = N; p.K = K;
-  p.kb_per_split = (total_kb + splits - 1) / splits;
-  p.splits = (total_kb + p.kb_per_split - 1) / p.kb_per_split;     // no empty split
+  p.parts = parts; p.part_stride = part_stride;
+  p.kb_per_split = (total_kb + splits * parts - 1) / (splits * parts);
+  if (parts == 1)
+    p.splits = (total_kb + p.kb_per_split - 1) / p.kb_per_split;     // no empty split
+  else if ((total_kb + p.kb_per_split - 1) / p.kb_per_split != splits * parts)
+    return cudaErrorInvalidValue;                                    // a range would be empty
+  else
+    p.splits = splits;
   p.dual_offset = dual_offset;
   p.epi = epi; p.bias = bias; p.bias_dtype = bias_dtype;
   p.out = out; p.ldo = ldo; p.error = nullptr;

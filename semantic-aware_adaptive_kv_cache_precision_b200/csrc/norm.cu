@@ -6,9 +6,11 @@
 // the positions whose logits are wanted). The order of the additions depends on
 // the row length alone, never on how many rows are in the batch.
 //
-// With `add` (fp32, same shape as x) the kernel first folds it into the stream,
-// x += add, stores x and normalises the sum: the residual add of the layer before
-// and this norm read and write the stream once instead of twice.
+// With `add` (fp32, `parts` tensors of x's shape, `part_stride` elements apart) the kernel
+// first folds them into the stream, x += add[0] + add[1] + ..., stores x and normalises
+// the sum: the residual add of the layer before and this norm read and write the stream
+// once instead of twice, and a product whose K ranges were summed apart is put together
+// here, in a fixed order.
 #include "common.cuh"
 
 namespace {
@@ -22,8 +24,8 @@ constexpr int kPerThread = 4;          // float4 loads per thread: rows up to 40
 template <typename W, typename Out, bool kAdd = false>
 __global__ void __launch_bounds__(kThreads)
 rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ add,
-               const int32_t* __restrict__ rows, const W* __restrict__ weight,
-               Out* __restrict__ out, int hidden, float eps) {
+               int parts, long long part_stride, const int32_t* __restrict__ rows,
+               const W* __restrict__ weight, Out* __restrict__ out, int hidden, float eps) {
   __shared__ float scratch[33];
   let_next_kernel_start();
   const bool fits = hidden <= kThreads * 4 * kPerThread && (hidden & 3) == 0;
@@ -51,11 +53,19 @@ rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ add,
       const int c = (i * kThreads + threadIdx.x) * 4;
       v[i] = c < hidden ? *reinterpret_cast<const float4*>(in + c) : make_float4(0, 0, 0, 0);
       if (kAdd && c < hidden) {
-        const float4 a = *reinterpret_cast<const float4*>(more + c);
-        v[i].x += a.x;
-        v[i].y += a.y;
-        v[i].z += a.z;
-        v[i].w += a.w;
+        float4 sum = *reinterpret_cast<const float4*>(more + c);
+#pragma unroll 4
+        for (int s = 1; s < parts; ++s) {
+          const float4 a = *reinterpret_cast<const float4*>(more + s * part_stride + c);
+          sum.x += a.x;
+          sum.y += a.y;
+          sum.z += a.z;
+          sum.w += a.w;
+        }
+        v[i].x += sum.x;
+        v[i].y += sum.y;
+        v[i].z += sum.z;
+        v[i].w += sum.w;
         *reinterpret_cast<float4*>(in + c) = v[i];
       }
       acc += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
@@ -76,7 +86,11 @@ rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ add,
   float acc = 0.f;
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
     float v = in[i];
-    if (kAdd) in[i] = v = v + more[i];   // (read again below by this thread)
+    if (kAdd) {                          // (read again below by this thread)
+      float sum = more[i];
+      for (int s = 1; s < parts; ++s) sum += more[s * part_stride + i];
+      in[i] = v = v + sum;
+    }
     acc += v * v;
   }
   const float scale = rsqrtf(block_sum(acc, scratch) / static_cast<float>(hidden) + eps);
@@ -86,12 +100,13 @@ rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ add,
 
 }  // namespace
 
-// `add`: null, or fp32 [n_rows, hidden] that is folded into x first (then `rows` must be
-// null, and the weight and the output bf16).
-SAKV_EXPORT int sakv_rmsnorm(float* x, const float* add, const int32_t* rows, const void* weight,
+// `add`: null, or `parts` fp32 tensors [n_rows, hidden], `part_stride` elements apart, that
+// are folded into x first (then `rows` must be null, and the weight and the output bf16).
+SAKV_EXPORT int sakv_rmsnorm(float* x, const float* add, int parts, long long part_stride, const int32_t* rows, const void* weight,
                              int weight_dtype, void* out, int out_dtype, int n_rows, int hidden,
                              float eps, cudaStream_t stream) {
-  if (n_rows < 0 || hidden <= 0 || (add && rows)) return cudaErrorInvalidValue;
+  if (n_rows < 0 || hidden <= 0 || (add && (rows || parts < 1)))
+    return cudaErrorInvalidValue;
   if (n_rows == 0) return 0;
   const int threads = kThreads;
   if (add) {
@@ -99,12 +114,12 @@ SAKV_EXPORT int sakv_rmsnorm(float* x, const float* add, const int32_t* rows, co
         out_dtype != SAKV_BF16)
       return cudaErrorInvalidValue;
     return launch_overlapped(rmsnorm_kernel<__nv_bfloat16, __nv_bfloat16, true>, dim3(n_rows),
-                             dim3(threads), 0, stream, 1, x, add, rows,
+                             dim3(threads), 0, stream, 1, x, add, parts, part_stride, rows,
                              (const __nv_bfloat16*)weight, (__nv_bfloat16*)out, hidden, eps);
   }
 #define LAUNCH(W, O)                                                                          \
   return launch_overlapped(rmsnorm_kernel<W, O>, dim3(n_rows), dim3(threads), 0, stream, 1, x, \
-                           (const float*)nullptr, rows, (const W*)weight, (O*)out,     \
+                           (const float*)nullptr, 0, 0LL, rows, (const W*)weight, (O*)out,     \
                            hidden, eps)
   if (weight_dtype == SAKV_F32 && out_dtype == SAKV_F32) LAUNCH(float, float);
   if (weight_dtype == SAKV_F32 && out_dtype == SAKV_BF16) LAUNCH(float, __nv_bfloat16);

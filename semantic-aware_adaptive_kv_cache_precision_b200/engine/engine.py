@@ -71,6 +71,7 @@ class Engine:
         self._graphs: dict = {}
         self._graph_pool = None
         self._decode_ran_eagerly = False
+        self.graph_failure = None
         self.ending = None
         self.endings: list = []
         self._loaded = False
@@ -194,7 +195,8 @@ class Engine:
             try:
                 with torch.cuda.graph(graph, pool=self._graph_pool):
                     out = self.model.logits(self.model.hidden(ctx, cache), ctx.want)
-            except Exception:
+            except Exception as exc:
+                self.graph_failure = repr(exc)      # kept for whoever wants to know why
                 # A part of this model does something a graph cannot hold (it reads a value
                 # back on the host, say, to route tokens). Nothing ran during the failed
                 # capture; from now on this engine runs its decode steps kernel by kernel.

@@ -90,11 +90,13 @@ class DecoderModel:
         x = ops.embed(step.token_ids, self.embed)
         written = set()
         pending = None          # a block's last output, not yet added to the stream
-        for call in self.spec.run_order:
+        last = len(self.spec.run_order) - 1
+        for i, call in enumerate(self.spec.run_order):
             view = cache.entry_view(call.cache, step.tables)
             block = self.blocks[call.block]
             if getattr(block, "carries_pending", False):
-                pending = block.forward(x, step, view, call.cache not in written, pending)
+                pending = block.forward(x, step, view, call.cache not in written, pending,
+                                        leave_pending=i < last)
             else:
                 if pending is not None:
                     ops.add_into(x, pending)

@@ -20,7 +20,7 @@ from .attention import (attention_decode, attention_prefill, attention_prefill_t
 __all__ = ["CACHE_BLOCK", "KernelError", "embed", "rms_norm", "rope_store", "attention_plain",
            "attention_decode", "attention_prefill", "attention_prefill_tc", "tc_prefill_takes", "plan_wide_tiles", "upload_wide_plan",
            "decode_splits", "fast_path_takes",
-           "kernel_errors", "gated_silu", "gated_up", "gemm_tc", "add_into", "linear", "choose", "prefetch_l2", "Deferred"]
+           "kernel_errors", "gated_silu", "gated_up", "gemm_tc", "add_into", "linear", "choose", "Deferred"]
 
 
 def _check(cond: bool, message: str) -> None:
@@ -46,8 +46,8 @@ def embed(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor | None = Non
 def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch.dtype,
              rows: torch.Tensor | None = None, add: torch.Tensor | None = None) -> torch.Tensor:
     """RMSNorm of rows of fp32 `x`; with `rows` (int32), of those rows only. With `add`
-    (fp32, x's shape; bf16 weight and output) `x += add` happens first, in the same kernel,
-    and x keeps the sum."""
+    (fp32, x's shape or [parts, *x's shape]; bf16 weight and output) `x += add` (`+=
+    add.sum(0)`, in order) happens first, in the same kernel, and x keeps the sum."""
     require_cuda(x, weight, rows, add)
     _check(x.dtype == torch.float32 and x.dim() == 2 and x.is_contiguous(), "x: fp32 [T, hidden]")
     hidden = x.shape[1]
@@ -58,23 +58,15 @@ def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch
                "rows: int32 [R]")
         n = rows.numel()
     if add is not None:
-        _check(rows is None and add.dtype == torch.float32 and add.shape == x.shape
-               and add.is_contiguous() and weight.dtype == torch.bfloat16
-               and out_dtype == torch.bfloat16, "add: fp32 like x, bf16 weight and output, no rows")
+        _check(rows is None and add.dtype == torch.float32 and add.is_contiguous()
+               and (add.shape == x.shape or (add.dim() == 3 and add.shape[1:] == x.shape))
+               and weight.dtype == torch.bfloat16 and out_dtype == torch.bfloat16,
+               "add: fp32 like x or [parts, *x.shape], bf16 weight and output, no rows")
+    parts = add.shape[0] if add is not None and add.dim() == 3 else 1
     out = torch.empty((n, hidden), dtype=out_dtype, device=x.device)
-    call("sakv_rmsnorm", ptr(x), ptr(add), ptr(rows), ptr(weight), dtype_code(weight.dtype), ptr(out),
+    call("sakv_rmsnorm", ptr(x), ptr(add), parts, x.numel(), ptr(rows), ptr(weight), dtype_code(weight.dtype), ptr(out),
          dtype_code(out_dtype), n, hidden, float(eps))
     return out
-
-
-def prefetch_l2(t: torch.Tensor) -> None:
-    """Ask the L2 cache for a tensor's bytes (weights that a kernel a few launches on will
-    stream); returns at once and runs beside the kernel before it."""
-    require_cuda(t)
-    size = t.numel() * t.element_size()
-    if not t.is_contiguous() or t.data_ptr() % 16 or size % 16:
-        return
-    call("sakv_prefetch_l2", ptr(t), size)
 
 
 def rope_store(qkv: torch.Tensor, positions: torch.Tensor, token_seq: torch.Tensor,
@@ -145,8 +137,16 @@ def gated_silu(gate_up: torch.Tensor) -> torch.Tensor:
 
 
 def add_into(acc: torch.Tensor, y: torch.Tensor) -> None:
-    """`acc += y` with `acc` fp32."""
+    """`acc += y` with `acc` fp32; `y` of acc's shape, or [parts, *acc.shape], whose parts are
+    summed first, in order (as `rms_norm(add=...)` does)."""
     require_cuda(acc, y)
+    if y.dim() == acc.dim() + 1:
+        total = y[0]
+        if y.shape[0] > 1:
+            total = y[0].clone()
+            for part in y[1:]:
+                add_into(total, part)
+        y = total
     _check(acc.dtype == torch.float32 and acc.is_contiguous() and y.is_contiguous()
            and acc.shape == y.shape, "acc: fp32, same shape as y, both contiguous")
     call("sakv_add_into", ptr(acc), ptr(y), dtype_code(y.dtype), acc.numel())

@@ -24,8 +24,7 @@ SIGNATURES = {
     "sakv_embed": ("elementwise", [P, P, I, P, I, I, I, P]),
     "sakv_gated_silu": ("elementwise", [P, P, I, I, I, P]),
     "sakv_add_into": ("elementwise", [P, P, I, L, P]),
-    "sakv_prefetch_l2": ("elementwise", [P, L, P]),
-    "sakv_rmsnorm": ("norm", [P, P, P, P, I, P, I, I, I, F, P]),
+    "sakv_rmsnorm": ("norm", [P, P, I, L, P, P, I, P, I, I, I, F, P]),
     "sakv_rope_store": ("rope", [P, I, L, P, P, P, I, P, P, I, P, P, I, I, I, I, I, P]),
     "sakv_attention_plain": ("attention_plain",
                              [P, I, L, P, P, P, P, P, P, I, I, I, I, I, F, I, P]),
@@ -37,7 +36,7 @@ SIGNATURES = {
                                [P, P, P, L, P, P, I, P, P, I, I, I, I, F, I, P]),
     "sakv_prefill_attention_tc": ("attention_prefill_tc",
                                   [P, P, P, P, P, I, P, I, P, P, P, P, I, I, I, I, F, I, P]),
-    "sakv_gemm_tc": ("gemm_tc", [P, P, I, I, I, I, I, I, I, P, I, P, L, P]),
+    "sakv_gemm_tc": ("gemm_tc", [P, P, I, I, I, I, I, I, I, I, P, I, P, L, L, P]),
 }
 
 #: functions without a stream argument: (library, argument types)

@@ -13,6 +13,7 @@ SM_COUNT = 148
 EPI_BF16, EPI_F32, EPI_ACCUM, EPI_GATED = 0, 1, 2, 3
 
 _weight_maps: dict = {}
+MAX_PARTS = 16      # K ranges whose sums the reader adds
 MAX_SPLITS = 8                # blocks of one cluster
 
 
@@ -82,21 +83,44 @@ def choose_splits(n_tiles: int, m_tiles: int, k: int, mt: int = 16, dual: bool =
     return best
 
 
+def choose_parts(m: int, n: int, k: int) -> tuple:
+    """(parts, splits) for a product whose result may be left as the sums of `parts` K
+    ranges for the reader to add, each range split over a cluster of `splits` blocks; (1, 0)
+    when the product is better added where it is made. Measured at 8 tokens, N = 1536, K =
+    8960: two ranges over clusters of 8 take 8.2 us against 11.1 us for one cluster of 8
+    adding into the stream, and the norm that adds two sums takes 0.6 us longer; for K =
+    1536 nothing is gained."""
+    mt = token_tile(m, False)
+    tiles = -(-n // 128) * -(-m // mt)
+    steps = -(-k // 64)
+    if tiles * 8 * 2 > SM_COUNT * 3 // 2 or steps < 64:
+        return 1, 0
+    per = -(-steps // 16)
+    if -(-steps // per) != 16:
+        return 1, 0
+    return 2, 8
+
+
 def gemm(x: torch.Tensor, weight: torch.Tensor, bias, epi: int, out: torch.Tensor,
-         n: int, dual_offset: int = 0, splits: int | None = None) -> torch.Tensor:
+         n: int, dual_offset: int = 0, splits: int | None = None, parts: int = 1) -> torch.Tensor:
     """`out` is written (EPI_BF16, EPI_F32, EPI_GATED) or added to (EPI_ACCUM); `n` is the
-    number of output columns (rows of `weight`, or half of them for EPI_GATED)."""
+    number of output columns (rows of `weight`, or half of them for EPI_GATED). With
+    `parts` > 1 (EPI_F32, `out` [parts, M, n]) K is cut into that many ranges whose sums are
+    left apart in `out[i]`, with the bias in `out[0]`."""
     m, k = x.shape
     dual = epi == EPI_GATED
     mt = token_tile(m, dual)
     n_tiles, m_tiles = -(-n // 128), -(-m // mt)
-    if splits is None:
+    if parts > 1:
+        splits = 1 if splits is None else splits
+    elif splits is None:
         splits = choose_splits(n_tiles, m_tiles, k, mt, dual)
-    splits = plain_function("sakv_gemm_tc_splits")(k, splits)
+    if parts == 1:
+        splits = plain_function("sakv_gemm_tc_splits")(k, splits)
     x_raw, x_map = _make_map(x, mt)
-    call("sakv_gemm_tc", _weight_map(weight), x_map, m, n, k, mt, splits, epi, dual_offset,
+    call("sakv_gemm_tc", _weight_map(weight), x_map, m, n, k, mt, splits, parts, epi, dual_offset,
          ptr(bias), dtype_code(bias.dtype) if bias is not None else BF16, ptr(out),
-         out.stride(0))
+         out.stride(-2), out.stride(0) if parts > 1 else 0)
     return out
 
 

@@ -54,10 +54,11 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = No
     With `accumulate_into` (fp32 [T, N]) the product is added to it in fp32 and it
     is returned; otherwise a new [T, N] tensor of `out_dtype` (default: x's type).
 
-    With `may_defer` as well, a product that the library computed into a tensor of its own
-    is not added: the call returns `Deferred(delta)` with the fp32 product, and the caller
-    owes `accumulate_into += delta` (the norm that reads the sum next can do it on its way,
-    `rms_norm(..., add=delta)`). Kernels that add in their epilogue return the accumulator.
+    With `may_defer` as well, a product that lies in a tensor of its own is not added: the
+    call returns `Deferred(delta)` with the fp32 product [T, N], or with the sums of several K
+    ranges [parts, T, N], and the caller owes `accumulate_into += delta` (`+= delta.sum(0)`);
+    the norm that reads the sum next can do it on its way, `rms_norm(..., add=delta)`.
+    Kernels that add in their epilogue return the accumulator.
     """
     require_cuda(x, weight, bias, accumulate_into)
     if x.dim() != 2 or weight.dim() != 2 or x.shape[1] != weight.shape[1]:
@@ -90,6 +91,12 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = No
     if tokens <= TC_MAX_TOKENS and gemm_tc.takes(xb, weight) and \
             (bias is None or bias.dtype in (torch.bfloat16, torch.float32)):
         if accumulate_into is not None:
+            parts, splits = gemm_tc.choose_parts(tokens, n, k) \
+                if may_defer and acc.is_contiguous() else (1, 0)
+            if parts > 1:      # few row tiles, long K: ranges summed apart, added by the reader
+                sums = torch.empty((parts, tokens, n), dtype=torch.float32, device=x.device)
+                return Deferred(gemm_tc.gemm(xb, weight, bias, gemm_tc.EPI_F32, sums, n,
+                                             splits=splits, parts=parts))
             return gemm_tc.gemm(xb, weight, bias, gemm_tc.EPI_ACCUM, acc, n)
         if out_dtype == torch.float32:
             out = torch.empty((tokens, n), dtype=torch.float32, device=x.device)

@@ -37,10 +37,10 @@ class PreNormBlock(Part):
     # it to the stream (`defer=True`); the norm that reads the stream next adds it on its way
     # if it has `folds_add`, so the stream is read and written once instead of twice. What the
     # feed-forward hands back leaves the block as `pending`: whoever runs the blocks gives it
-    # to the next one, or adds it to the stream at the end.
+    # to the next one, or asks the last one not to leave any (`leave_pending=False`).
     carries_pending = True
 
-    def forward(self, x, step, view, write_cache=True, pending=None):
+    def forward(self, x, step, view, write_cache=True, pending=None, leave_pending=True):
         h = _normed(self.mixer_norm, x, pending)
         if getattr(self.mixer, "can_defer", False):
             pending = self.mixer.forward(h, step, view, x, write_cache, defer=True)
@@ -48,7 +48,7 @@ class PreNormBlock(Part):
             self.mixer.forward(h, step, view, x, write_cache)
             pending = None
         h = _normed(self.ffn_norm, x, pending)
-        if getattr(self.ffn, "can_defer", False):
+        if leave_pending and getattr(self.ffn, "can_defer", False):
             return self.ffn.forward(h, step, x, defer=True)
         self.ffn.forward(h, step, x)
         return None

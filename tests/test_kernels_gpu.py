@@ -502,6 +502,61 @@ def test_gemm_tc_epilogues(M, N, K, splits):
     assert gemm_tc.error_word() == 0
 
 
+@pytest.mark.parametrize("M,N,K,parts,splits", [
+    (8, 1536, 8960, 12, 1), (8, 1536, 1536, 12, 1), (64, 1536, 8960, 6, 2), (3, 200, 328, 3, 2),
+    (17, 130, 2048, 16, 1), (1, 128, 128, 2, 1)])
+def test_gemm_tc_k_ranges_summed_apart(M, N, K, parts, splits):
+    """K cut into ranges whose sums are left apart: the bias is in the first, their sum is
+    the product, and the norm that adds them on its way gives what the separate steps give."""
+    from semantic_aware_adaptive_kv_cache_precision_b200.ops import gemm_tc
+    rng = np.random.default_rng(M + N + K)
+    x = dev(rng.standard_normal((M, K)), torch.bfloat16)
+    w = dev(rng.standard_normal((N, K)), torch.bfloat16)
+    b = dev(rng.standard_normal(N), torch.bfloat16)
+    sums = torch.full((parts, M, N), float("nan"), dtype=torch.float32, device=DEV)
+    gemm_tc.gemm(x, w, b, gemm_tc.EPI_F32, sums, N, splits=splits, parts=parts)
+    assert gemm_tc.error_word() == 0
+    want = host(x) @ host(w).T + host(b)
+    got = host(sums)
+    assert np.isfinite(got).all()
+    assert np.abs(got.sum(0) - want).max() <= 2e-6 * np.abs(want).max() * np.sqrt(K) + 1e-6
+    per = -(-(-(-K // 64)) // (parts * splits)) * 64 * splits         # columns of K per part
+    for i in range(parts):
+        part = host(x)[:, i * per:(i + 1) * per] @ host(w)[:, i * per:(i + 1) * per].T
+        if i == 0:
+            part = part + host(b)
+        assert np.abs(got[i] - part).max() <= 2e-6 * np.abs(want).max() * np.sqrt(K) + 1e-6
+    # the reader's side
+    stream = dev(rng.standard_normal((M, N)))
+    weight = dev(1 + 0.1 * rng.standard_normal(N), torch.bfloat16)
+    apart = stream.clone()
+    ops.add_into(apart, sums)
+    want_normed = ops.rms_norm(apart, weight, 1e-5, torch.bfloat16)
+    got_normed = ops.rms_norm(stream, weight, 1e-5, torch.bfloat16, add=sums)
+    assert torch.equal(stream, apart) and torch.equal(got_normed, want_normed)
+
+
+def test_linear_hands_back_k_ranges_only_when_asked():
+    rng = np.random.default_rng(5)
+    x = dev(rng.standard_normal((8, 8960)), torch.bfloat16)
+    w = dev(rng.standard_normal((1536, 8960)) * 0.02, torch.bfloat16)
+    acc = dev(rng.standard_normal((8, 1536)))
+    kept = acc.clone()
+    out = ops.linear(x, w, accumulate_into=acc, may_defer=True)
+    assert isinstance(out, ops.Deferred) and out.delta.dim() == 3 and torch.equal(acc, kept)
+    same = ops.linear(x, w, accumulate_into=acc)
+    assert same is acc
+    want = host(kept) + host(x) @ host(w).T
+    np.testing.assert_allclose(host(acc), want, rtol=0, atol=1e-4)
+    ops.add_into(kept, out.delta)
+    np.testing.assert_allclose(host(kept), want, rtol=0, atol=1e-4)
+    # many row tiles: nothing to gain, the product is added where it is made
+    wide = dev(rng.standard_normal((17920, 1536)) * 0.02, torch.bfloat16)
+    acc2 = torch.zeros((8, 17920), device=DEV)
+    assert ops.linear(dev(rng.standard_normal((8, 1536)), torch.bfloat16), wide,
+                      accumulate_into=acc2, may_defer=True) is acc2
+
+
 @pytest.mark.parametrize("M,I,K", [(1, 128, 64), (8, 8960, 1536), (50, 256, 200), (128, 384, 1536)])
 def test_gemm_tc_gated(M, I, K):
     rng = np.random.default_rng(M + I + K)
