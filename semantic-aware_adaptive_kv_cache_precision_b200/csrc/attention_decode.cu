@@ -65,7 +65,10 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap k_map,
     tma::prefetch_map(&k_map);
     tma::prefetch_map(&v_map);
   }
-  wait_for_previous_kernel();        // lengths, block lists, queries and the newest keys
+  // The lengths and block lists are the step's inputs, written before its first kernel
+  // started, and every cached key but the newest was written by an earlier step: all of
+  // that is read, and those tiles are on their way, before this kernel waits for the one
+  // before it, which wrote the queries and the newest key and value.
   const int kv_len = seq_lens[b];
   const int first_key = (window > 0 && kv_len - window > 0) ? kv_len - window : 0;
   const int first_tile = first_key / KT;
@@ -74,7 +77,6 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap k_map,
   const int per_split = (count + splits - 1) / splits;
   const int t0 = first_tile + split * per_split;
   const int t1 = min(n_tiles, t0 + per_split);
-  __syncthreads();
 
   // Tile i of this split goes to stage i % kStages. Lane 0 of warp 0 keeps the ring full:
   // kStages tiles to begin with, then tile i + kStages once every warp has let go of tile i.
@@ -90,8 +92,13 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap k_map,
     }
   };
   const int n_key_tiles = max(t1 - t0, 0);
+  const int newest = n_tiles - 1 - t0;         // the tile that holds the newest key, if in this split
   if (threadIdx.x == 0)
-    for (int i = 0; i < min(kStages, n_key_tiles); ++i) request(i);
+    for (int i = 0; i < min(kStages, n_key_tiles); ++i)
+      if (i != newest) request(i);
+  wait_for_previous_kernel();
+  if (threadIdx.x == 0 && newest >= 0 && newest < min(kStages, n_key_tiles)) request(newest);
+  __syncthreads();
 
   // ---- compute warps ------------------------------------------------------------
   // Query rows of this warp's m16 tile: row r = head g*group + r, rows >= group are zero.
@@ -269,23 +276,42 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap k_map,
   }
 }
 
-// out[b, h, :] = sum_s w_s o_s / sum_s w_s l_s with w_s = exp2(m_s - max m)
+// out[b, h, :] = sum_s w_s o_s / sum_s w_s l_s with w_s = exp2(m_s - max m). The splits are
+// taken sixteen at a time, with all of a round's loads (maxima, sums, outputs) in flight
+// together, and rounds are merged like tiles of an online softmax: up to 16 splits cost one
+// memory round trip.
 __global__ void combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                __nv_bfloat16* __restrict__ out, int splits, int head_dim) {
   let_next_kernel_start();
   wait_for_previous_kernel();
+  constexpr int kRound = 16;
   const long long bh = blockIdx.x;
-  const float* ml = part_ml + bh * splits * 2;
-  float big = -INFINITY;
-  for (int s = 0; s < splits; ++s) big = fmaxf(big, ml[2 * s]);
-  float total = 0.f;
-  for (int s = 0; s < splits; ++s)
-    total += (ml[2 * s] == -INFINITY) ? 0.f : exp2f(ml[2 * s] - big) * ml[2 * s + 1];
+  const float2* ml = reinterpret_cast<const float2*>(part_ml) + bh * splits;
   for (int dim = threadIdx.x; dim < head_dim; dim += blockDim.x) {
-    float acc = 0.f;
-    for (int s = 0; s < splits; ++s) {
-      const float w = (ml[2 * s] == -INFINITY) ? 0.f : exp2f(ml[2 * s] - big);
-      acc += w * part_o[(bh * splits + s) * head_dim + dim];
+    float big = -INFINITY, total = 0.f, acc = 0.f;
+    for (int s0 = 0; s0 < splits; s0 += kRound) {
+      float2 v[kRound];
+      float o[kRound];
+#pragma unroll
+      for (int j = 0; j < kRound; ++j) {
+        const bool live = s0 + j < splits;
+        v[j] = live ? ml[s0 + j] : make_float2(-INFINITY, 0.f);
+        o[j] = live ? part_o[(bh * splits + s0 + j) * head_dim + dim] : 0.f;
+      }
+      float round_max = big;
+#pragma unroll
+      for (int j = 0; j < kRound; ++j) round_max = fmaxf(round_max, v[j].x);
+      if (round_max == -INFINITY) continue;
+      const float keep = exp2f(big - round_max);          // 0 the first time
+      total *= keep;
+      acc *= keep;
+      big = round_max;
+#pragma unroll
+      for (int j = 0; j < kRound; ++j) {
+        const float w = exp2f(v[j].x - big);              // 0 for a split that saw no key
+        total += w * v[j].y;
+        acc += w * o[j];
+      }
     }
     out[bh * head_dim + dim] = __float2bfloat16_rn(acc / total);
   }
@@ -344,7 +370,7 @@ SAKV_EXPORT int sakv_decode_attention(const void* k_map, const void* v_map, cons
                                       int kv_heads, int head_dim, int splits, float scale,
                                       int window, cudaStream_t stream) {
   if (sequences < 0 || heads <= 0 || kv_heads <= 0 || heads % kv_heads || heads / kv_heads > 16 ||
-      splits < 1 || max_blocks <= 0 || (splits > 1 && (!part_o || !part_ml)))
+      splits < 1 || max_blocks <= 0 || (splits > 1 && (!part_o || !part_ml || (reinterpret_cast<uintptr_t>(part_ml) & 7))))
     return cudaErrorInvalidValue;
   if (sequences == 0) return 0;
   if (sequences > 65535 || kv_heads > 65535) return cudaErrorInvalidValue;

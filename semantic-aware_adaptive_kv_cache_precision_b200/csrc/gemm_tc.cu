@@ -99,15 +99,17 @@ __device__ __forceinline__ float bias_at(const Params& p, int n) {
                                   : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.bias)[n]);
 }
 
+// (the epilogue's kind is a template argument: the choice is made once, not per element)
+template <int kEpi>
 __device__ __forceinline__ void finish(const Params& p, int part, int m, int n, float c, float up,
                                        float bias) {
   if (m >= p.M || n >= p.N) return;
   const long long at = (long long)m * p.ldo + n + part * p.part_stride;
-  if (p.epi == EPI_BF16) {
+  if (kEpi == EPI_BF16) {
     reinterpret_cast<__nv_bfloat16*>(p.out)[at] = __float2bfloat16_rn(c + bias);
-  } else if (p.epi == EPI_F32) {
+  } else if (kEpi == EPI_F32) {
     reinterpret_cast<float*>(p.out)[at] = c + bias;
-  } else if (p.epi == EPI_ACCUM) {
+  } else if (kEpi == EPI_ACCUM) {
     // one block adds to each element exactly once, so the sum is the same every time; the
     // reduction instruction spares the thread the round trip of reading the old value
     atomicAdd(reinterpret_cast<float*>(p.out) + at, c + bias);
@@ -123,9 +125,10 @@ __device__ __forceinline__ void finish(const Params& p, int part, int m, int n, 
 // decode step: 2, 8 and 16 columns at a time are all slower). The usual cluster sizes (S =
 // 2, 4, 8) are compiled apart, so that the loops over the cluster unroll to its real size
 // (the decode step at 8 sequences: 1.68 -> 1.61 ms); S = 0 is any other size.
-template <int MT, bool kDual, int S>
+template <int MT, int kEpi, int S>
 __device__ __forceinline__ void reduce_columns(const Params& p, uint32_t base, int split,
                                                int k_part, int m0, int n, int row, float bias) {
+  constexpr bool kDual = kEpi == EPI_GATED;
   constexpr int kS = S > 0 ? S : kMaxSplits;
   constexpr int kBatch = 4;
   const int splits = S > 0 ? S : p.splits;
@@ -155,15 +158,16 @@ __device__ __forceinline__ void reduce_columns(const Params& p, uint32_t base, i
         acc += part[j][s];
         if (kDual) up += part_up[j][s];
       }
-      finish(p, k_part, m0 + c, n, acc, up, bias);
+      finish<kEpi>(p, k_part, m0 + c, n, acc, up, bias);
     }
   }
 }
 
-template <int MT, bool kDual>
+template <int MT, int kEpi>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant__ CUtensorMap x_map,
                const Params p) {
+  constexpr bool kDual = kEpi == EPI_GATED;
   using C = Cfg<MT, kDual>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -220,15 +224,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
       for (int i = 0; i < ahead; ++i)
         tma::load_2d(smem + i * C::kStageBytes + (kDual ? 2 : 1) * kWTile, &x_map,
                      (kb0 + i) * BK, m0, &full[i]);
+      // (the ring's position is counted, not divided out: `stages` is a run-time number and
+      // this lane's instructions are the pipeline's pace)
+      int stage = ahead == stages ? 0 : ahead, phase = 0;
       for (int i = ahead; i < n_kb; ++i) {
-        const int stage = i % stages;
-        if (!tma::mbar_wait(&empty[stage], ((i / stages) - 1) & 1, p.error, 301)) break;
+        if (!tma::mbar_wait(&empty[stage], phase, p.error, 301)) break;
         uint8_t* dst = smem + stage * C::kStageBytes;
         const int x = (kb0 + i) * BK;
         tma::mbar_expect_tx(&full[stage], C::kStageBytes);
         tma::load_2d(dst, &w_map, x, n0, &full[stage]);
         if (kDual) tma::load_2d(dst + kWTile, &w_map, x, p.dual_offset + n0, &full[stage]);
         tma::load_2d(dst + (kDual ? 2 : 1) * kWTile, &x_map, x, m0, &full[stage]);
+        if (++stage == stages) {
+          stage = 0;
+          phase ^= 1;
+        }
       }
     }
   } else if (warp == 1) {
@@ -236,9 +246,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
     if (lane == 0) {
       constexpr uint32_t idesc = tc::idesc_bf16_f32(BM, MT);
       bool ok = true;
+      int stage = 0, phase = 0;
       for (int i = 0; i < n_kb && ok; ++i) {
-        const int stage = i % stages;
-        ok = tma::mbar_wait(&full[stage], (i / stages) & 1, p.error, 302);
+        ok = tma::mbar_wait(&full[stage], phase, p.error, 302);
         if (!ok) break;
         tc::fence_after_sync();
         const uint32_t a = tma::smem_u32(smem + stage * C::kStageBytes);
@@ -252,6 +262,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
                        i > 0 || k > 0);
         }
         tc::commit(&empty[stage]);      // the stage is free once these MMAs have read it
+        if (++stage == stages) {
+          stage = 0;
+          phase ^= 1;
+        }
       }
       tc::commit(accum);                // the accumulator is complete
     }
@@ -274,7 +288,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
           if (kDual) tc::ld_32x32b_x16(taddr + MT + c, u);
 #pragma unroll
           for (int j = 0; j < 16; ++j)
-            finish(p, k_part, m0 + c + j, n, v[j], kDual ? u[j] : 0.f, bias);
+            finish<kEpi>(p, k_part, m0 + c + j, n, v[j], kDual ? u[j] : 0.f, bias);
         }
       }
     } else if (ok) {
@@ -300,13 +314,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
       const uint32_t base = tma::smem_u32(smem);
       // token columns split, split + splits, ... are finished by this block
       if (p.splits == 2)
-        reduce_columns<MT, kDual, 2>(p, base, split, k_part, m0, n, row, bias);
+        reduce_columns<MT, kEpi, 2>(p, base, split, k_part, m0, n, row, bias);
       else if (p.splits == 4)
-        reduce_columns<MT, kDual, 4>(p, base, split, k_part, m0, n, row, bias);
+        reduce_columns<MT, kEpi, 4>(p, base, split, k_part, m0, n, row, bias);
       else if (p.splits == 8)
-        reduce_columns<MT, kDual, 8>(p, base, split, k_part, m0, n, row, bias);
+        reduce_columns<MT, kEpi, 8>(p, base, split, k_part, m0, n, row, bias);
       else
-        reduce_columns<MT, kDual, 0>(p, base, split, k_part, m0, n, row, bias);
+        reduce_columns<MT, kEpi, 0>(p, base, split, k_part, m0, n, row, bias);
     }
     cluster_sync_all();       // nobody leaves while a peer may still read its shared memory
   }
@@ -319,13 +333,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
 
 __device__ int g_error;
 
-template <int MT, bool kDual>
+template <int MT, int kEpi>
 int launch(const CUtensorMap* w_map, const CUtensorMap* x_map, Params p, int n_tiles, int m_tiles,
            cudaStream_t stream) {
+  constexpr bool kDual = kEpi == EPI_GATED;
   using C = Cfg<MT, kDual>;
   static bool configured = false;
   if (!configured) {
-    const cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<MT, kDual>,
+    const cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<MT, kEpi>,
                                                cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                C::smem_bytes(C::kMaxStages) > 227 * 1024
                                                    ? 227 * 1024 : C::smem_bytes(C::kMaxStages));
@@ -336,7 +351,7 @@ int launch(const CUtensorMap* w_map, const CUtensorMap* x_map, Params p, int n_t
   while (C::smem_bytes(p.stages) > 227 * 1024) --p.stages;
   if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p.error), g_error) != cudaSuccess)
     return cudaErrorInvalidValue;
-  return launch_overlapped(gemm_tc_kernel<MT, kDual>, dim3(n_tiles, m_tiles, p.splits * p.parts),
+  return launch_overlapped(gemm_tc_kernel<MT, kEpi>, dim3(n_tiles, m_tiles, p.splits * p.parts),
                            dim3(kThreads), (size_t)C::smem_bytes(p.stages), stream, p.splits,
                            *w_map, *x_map, p);
 }
@@ -391,10 +406,12 @@ SAKV_EXPORT int sakv_gemm_tc(const void* w_map, const void* x_map, int M, int N,
   const CUtensorMap* xm = (const CUtensorMap*)x_map;
 #define GO(MT_)                                                                   \
   if (mt == MT_)                                                                  \
-    return dual ? launch<MT_, true>(wm, xm, p, n_tiles, m_tiles, stream)          \
-                : launch<MT_, false>(wm, xm, p, n_tiles, m_tiles, stream)
+    return dual ? launch<MT_, EPI_GATED>(wm, xm, p, n_tiles, m_tiles, stream)     \
+         : epi == EPI_BF16 ? launch<MT_, EPI_BF16>(wm, xm, p, n_tiles, m_tiles, stream)   \
+         : epi == EPI_F32 ? launch<MT_, EPI_F32>(wm, xm, p, n_tiles, m_tiles, stream)     \
+                          : launch<MT_, EPI_ACCUM>(wm, xm, p, n_tiles, m_tiles, stream)
   GO(16); GO(32); GO(64); GO(128);
-  if (mt == 256 && !dual) return launch<256, false>(wm, xm, p, n_tiles, m_tiles, stream);
+  if (!dual) GO(256);
 #undef GO
   return cudaErrorInvalidValue;
 }
@@ -428,9 +445,9 @@ SAKV_EXPORT int sakv_gemm_tc_max_clusters(int mt, int dual, int splits) {
     using C = Cfg<MT_, D_>;                                                                    \
     const int bytes = C::smem_bytes(C::stages_for(1));                                         \
     config.dynamicSmemBytes = bytes > 227 * 1024 ? 227 * 1024 : bytes;                         \
-    cudaFuncSetAttribute(gemm_tc_kernel<MT_, D_>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+    cudaFuncSetAttribute(gemm_tc_kernel<MT_, (D_ ? EPI_GATED : EPI_BF16)>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
                          (int)config.dynamicSmemBytes);                                        \
-    if (cudaOccupancyMaxActiveClusters(&clusters, gemm_tc_kernel<MT_, D_>, &config) !=         \
+    if (cudaOccupancyMaxActiveClusters(&clusters, gemm_tc_kernel<MT_, (D_ ? EPI_GATED : EPI_BF16)>, &config) !=         \
         cudaSuccess)                                                                           \
       clusters = 0;                                                                            \
     cudaGetLastError();                                                                        \

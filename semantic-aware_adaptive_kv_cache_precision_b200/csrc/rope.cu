@@ -76,13 +76,16 @@ __global__ void rope_store_bf16_vec_kernel(__nv_bfloat16* __restrict__ qkv, long
                                            __nv_bfloat16* __restrict__ v_cache, int heads,
                                            int kv_heads, int head_dim, int write_cache) {
   let_next_kernel_start();
-  wait_for_previous_kernel();
+  // Positions, sequence indices and block lists are the step's inputs, written before its
+  // first kernel started: these dependent loads are done while the kernel before this one
+  // (which writes qkv) is still running.
   const int t = blockIdx.x;
   const int pos = positions[t];
   const int half = rot / 2;
   const int block = write_cache
                         ? block_table[(long long)token_seq[t] * max_blocks + pos / kCacheBlock]
                         : -1;
+  wait_for_previous_kernel();
   const int per_head = head_dim / 8;                 // 16-byte pieces per head
   const int rot_pieces = half / 8;                   // pieces of the first half of the rotary part
   const int all_heads = heads + 2 * kv_heads;
