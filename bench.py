@@ -44,6 +44,17 @@ QWEN25_1P5B = {
     "tie_word_embeddings": True, "hidden_act": "silu", "torch_dtype": "bfloat16",
     "use_sliding_window": False, "eos_token_id": 151645,
 }
+#: the other shapes the reference is quoted on: only the sizes that differ
+SHAPES = {
+    "1.5b": ("Qwen2.5-1.5B shape", {}),
+    "7b": ("Qwen2.5-7B shape", {"hidden_size": 3584, "num_attention_heads": 28,
+                                "num_key_value_heads": 4, "intermediate_size": 18944,
+                                "vocab_size": 152064, "tie_word_embeddings": False}),
+    "32b": ("Qwen2.5-32B shape", {"num_hidden_layers": 64, "hidden_size": 5120,
+                                  "num_attention_heads": 40, "num_key_value_heads": 8,
+                                  "intermediate_size": 27648, "vocab_size": 152064,
+                                  "tie_word_embeddings": False}),
+}
 CONTEXT = 2048
 PREFILL_TOKENS = 2048
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
@@ -144,6 +155,8 @@ def reference_arm(args) -> int:
         print(json.dumps({"impl": "reference", "unavailable": why}))
         return 0
 
+    if getattr(args, "shape", "1.5b") != "1.5b":
+        return unavailable("the reference arm runs the headline's Qwen2.5-1.5B shape only")
     ref = os.path.join(ROOT, "baseline", "_ref")
     if not os.path.isdir(os.path.join(ref, "microinfer")):
         return unavailable("baseline/_ref is absent: the reference was not installed on this box")
@@ -221,7 +234,7 @@ def reference_arm(args) -> int:
     prefill_ms = statistics.median(prefill_s) * 1e3
     pk = peaks()
     print(json.dumps({
-        "metric": "decode tokens/s (Qwen2.5-1.5B shape, batch 8, 2048 cached tokens)",
+        "metric": f"decode tokens/s (Qwen2.5-1.5B shape, batch {args.batch}, {CONTEXT} cached tokens)",
         "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W,
         "ms_per_step": round(decode_s / K * 1e3, 4), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "fp16", "impl": "reference",
@@ -319,7 +332,11 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=None,
                     help="fewer layers than the configuration has (recorded in config)")
-    ap.add_argument("--no-points", action="store_true", help="skip batch 1 and 64")
+    ap.add_argument("--shape", default="1.5b", choices=sorted(SHAPES),
+                    help="layer sizes (default: the headline's Qwen2.5-1.5B shape)")
+    ap.add_argument("--context", type=int, default=CONTEXT, help="cached tokens per sequence")
+    ap.add_argument("--points", default="1,64", help="further batch sizes to decode at")
+    ap.add_argument("--no-points", action="store_true", help="skip the further batch sizes")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-check", action="store_true",
                     help="skip the comparison of the bf16 logits with the fp32 path's")
@@ -340,15 +357,18 @@ def main() -> int:
     from semantic_aware_adaptive_kv_cache_precision_b200 import sampling
     from semantic_aware_adaptive_kv_cache_precision_b200.ops import _lib
 
-    raw = dict(QWEN25_1P5B)
+    model_name, sizes = SHAPES[args.shape]
+    raw = {**QWEN25_1P5B, **sizes}
     full_layers = raw["num_hidden_layers"]
     if args.layers:
         raw["num_hidden_layers"] = args.layers
     cfg = sakv.config_from_dict(raw)
     K, W = args.steps, args.warmup
-    batches = [args.batch] + ([] if args.no_points else [b for b in (1, 64) if b != args.batch])
+    context = args.context
+    further = [int(b) for b in args.points.split(",") if b]
+    batches = [args.batch] + ([] if args.no_points else [b for b in further if b != args.batch])
     most = max(batches)
-    room = -(-(CONTEXT + K + W + 8) // 64) * 64
+    room = -(-(context + K + W + 8) // 64) * 64
     engine = sakv.Engine(config=cfg, dtype="bfloat16", random_seed=0, max_batch=most,
                          max_tokens=most * room, max_step_tokens=8192).load_weights()
     pk = peaks()
@@ -356,11 +376,11 @@ def main() -> int:
     greedy = sampling.SamplingParams()
 
     def filled(batch: int):
-        """`batch` sequences that each hold CONTEXT cached tokens (a real prefill)."""
+        """`batch` sequences that each hold context cached tokens (a real prefill)."""
         slots = engine.open(batch)
         for begin in range(0, batch, 4):
             part = slots[begin:begin + 4]
-            engine.step(part, [rng.integers(0, cfg.vocab_size, CONTEXT) for _ in part],
+            engine.step(part, [rng.integers(0, cfg.vocab_size, context) for _ in part],
                         [[] for _ in part])
         return slots
 
@@ -394,7 +414,7 @@ def main() -> int:
     ms, launches, clocks = decode_run(args.batch, K, W)
     ms_per_step = ms / K
     value = args.batch * K / (ms / 1e3)
-    mid_context = CONTEXT + W + K // 2
+    mid_context = context + W + K // 2
     achieved = decode_bytes(cfg, args.batch, mid_context) / (ms_per_step / 1e3) / 1e9
 
     points = {}
@@ -427,7 +447,7 @@ def main() -> int:
     # -- end to end through Engine.generate: host tokens in, host tokens out ----------------
     e2e = None
     if not args.no_e2e:
-        prompts = [rng.integers(0, cfg.vocab_size, CONTEXT).tolist() for _ in range(args.batch)]
+        prompts = [rng.integers(0, cfg.vocab_size, context).tolist() for _ in range(args.batch)]
 
         def timed(new_tokens: int) -> float:
             torch.cuda.synchronize()
@@ -475,19 +495,20 @@ def main() -> int:
                  "mean_kl": float(f"{kl:.3e}"),
                  "max_abs_logit_diff": round(float(np.abs(got - want).max()), 4)}
 
+    weight_gb = decode_bytes(cfg, 0, 0) / 1e9
     line = {
-        "metric": "decode tokens/s (Qwen2.5-1.5B shape, batch 8, 2048 cached tokens)",
+        "metric": f"decode tokens/s ({model_name}, batch {args.batch}, {context} cached tokens)",
         "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W,
         "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic: random weights, random token ids",
         "impl": "ours",
-        "config": {"model": "Qwen2.5-1.5B shape", "layers": cfg.num_hidden_layers,
+        "config": {"model": model_name, "layers": cfg.num_hidden_layers,
                    "layers_of_model": full_layers, "hidden": cfg.hidden_size,
                    "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
                    "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size,
                    "vocab": cfg.vocab_size, "tied_head": cfg.tie_word_embeddings,
-                   "global_batch": args.batch, "seq_len": CONTEXT, "new_tokens": K,
-                   "parallelism": "single GPU", "l2": "weights (3.1 GB) exceed L2; no flush",
+                   "global_batch": args.batch, "seq_len": context, "new_tokens": K,
+                   "parallelism": "single GPU", "l2": f"weights ({weight_gb:.1f} GB) exceed L2; no flush",
                    "peaks": pk["source"]},
         "prefill": prefill,
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"],
