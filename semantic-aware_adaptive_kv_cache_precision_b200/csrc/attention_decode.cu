@@ -228,15 +228,16 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap k_map,
     l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
   }
   asm volatile("bar.sync 1, %0;" ::"n"(kComputeWarps * 32));   // every tile has been consumed
-  float* sm_o = reinterpret_cast<float*>(smem);                // [warp][16][D]
-  float* sm_m = sm_o + kComputeWarps * 16 * D;                 // [warp][16]
+  constexpr int kRow = D + 8;       // padded: the eight rows a warp stores at once miss each other's banks
+  float* sm_o = reinterpret_cast<float*>(smem);                // [warp][16][kRow]
+  float* sm_m = sm_o + kComputeWarps * 16 * kRow;              // [warp][16]
   float* sm_l = sm_m + kComputeWarps * 16;
   {
     const int r0 = lane >> 2, c = (lane & 3) * 2;
 #pragma unroll
     for (int nt = 0; nt < D / 8; ++nt) {
-      float* row0 = sm_o + (warp * 16 + r0) * D + nt * 8 + c;
-      float* row1 = row0 + 8 * D;
+      float* row0 = sm_o + (warp * 16 + r0) * kRow + nt * 8 + c;
+      float* row1 = row0 + 8 * kRow;
       row0[0] = o[nt][0]; row0[1] = o[nt][1];
       row1[0] = o[nt][2]; row1[1] = o[nt][3];
     }
@@ -261,7 +262,7 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap k_map,
     for (int dim = threadIdx.x; dim < D; dim += kComputeWarps * 32) {
       float acc = 0.f;
 #pragma unroll
-      for (int w = 0; w < kComputeWarps; ++w) acc += weight[w] * sm_o[(w * 16 + r) * D + dim];
+      for (int w = 0; w < kComputeWarps; ++w) acc += weight[w] * sm_o[(w * 16 + r) * kRow + dim];
       if (splits == 1) {
         out[((long long)b * heads + h) * D + dim] = __float2bfloat16_rn(acc / total);
       } else {
