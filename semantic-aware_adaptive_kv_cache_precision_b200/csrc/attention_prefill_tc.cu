@@ -237,16 +237,23 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap q_map,
       tma::mbar_arrive(&bar->s_free[bj]);
       const int key0 = (t0 + j) * KT;
       const bool needs_mask = key0 + KT - 1 > pos0 || (window > 0 && key0 < last_pos - window + 1);
-      float big = -INFINITY;
+      if (needs_mask) {
 #pragma unroll
-      for (int c = 0; c < KT; ++c) {
-        if (needs_mask) {
+        for (int c = 0; c < KT; ++c) {
           const int key = key0 + c;
           const bool seen = key <= pos && (window <= 0 || key > pos - window);
           s[c] = seen ? s[c] : -INFINITY;
         }
-        big = fmaxf(big, s[c]);
       }
+      // four chains of three-input maxima: the row is one thread's, and a single chain of 64
+      // would wait on itself (two warps a scheduler hide little)
+      float big4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+      for (int c = 0; c < KT; c += 8) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) big4[q] = mma::max3(big4[q], s[c + 2 * q], s[c + 2 * q + 1]);
+      }
+      const float big = fmaxf(fmaxf(big4[0], big4[1]), fmaxf(big4[2], big4[3]));
       m_true = fmaxf(m_true, big * scale_log2e);
       // P_{j-1} V_{j-1} must be done before P is overwritten and before O is touched
       if (j >= 1 && !tma::mbar_wait(&bar->pv_done, (j - 1) & 1, error, 408)) { ok = false; break; }
@@ -260,7 +267,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap q_map,
             float v[16];
             tc::ld_32x32b_x16(lane_base + kOCol + c, v);
 #pragma unroll
-            for (int i = 0; i < 16; ++i) v[i] *= factor;
+            for (int i = 0; i < 16; i += 2) mma::mul2(v[i], v[i + 1], factor);
             tc::st_32x32b_x16(lane_base + kOCol + c, v);
           }
           tc::fence_before_sync();
@@ -271,22 +278,26 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap q_map,
         }
       }
       const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
-      float sum = 0.f;
-      // P row, bf16, into the swizzled K-major layout of an A operand: 8 chunks of 8 keys
+      // P row, bf16, into the swizzled K-major layout of an A operand: 8 chunks of 8 keys.
+      // Exponents two at a time (one fma for both), four running sums.
+      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
       uint8_t* p_row = p_s + r * 128;
+      const float minus_m = -m_use;
 #pragma unroll
       for (int ch = 0; ch < KT / 8; ++ch) {
         uint32_t packed[4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-          const float p0 = mma::exp2_fast(fmaf(s[ch * 8 + 2 * i], scale_log2e, -m_use));
-          const float p1 = mma::exp2_fast(fmaf(s[ch * 8 + 2 * i + 1], scale_log2e, -m_use));
-          sum += p0 + p1;
+          float e0, e1;
+          mma::fma2(e0, e1, s[ch * 8 + 2 * i], s[ch * 8 + 2 * i + 1], scale_log2e, minus_m);
+          const float p0 = mma::exp2_fast(e0), p1 = mma::exp2_fast(e1);
+          mma::add2(sum4[(i & 1) * 2], sum4[(i & 1) * 2 + 1], p0, p1);
           packed[i] = mma::pack_bf16(p0, p1);
         }
         *reinterpret_cast<uint4*>(p_row + ((ch ^ (r & 7)) << 4)) =
             make_uint4(packed[0], packed[1], packed[2], packed[3]);
       }
+      const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
       l += sum;
       // the sequence's last block: value rows past its end are stale; zero them before P.V
       const int valid = kv_len - key0;
@@ -382,6 +393,7 @@ __global__ void fold_partials_kernel(const int4* __restrict__ folds, const float
 }
 
 __device__ int g_error;
+
 
 }  // namespace
 
