@@ -41,9 +41,8 @@ constexpr int kThreads = 192;
 constexpr int kQBytes = QT * D * 2;              // two boxes of [128 x 64]
 constexpr int kTileBytes = KT * D * 2;           // K or V: two boxes of [64 x 64]
 constexpr int kStageBytes = 2 * kTileBytes;
-constexpr int kPBytes = QT * KT * 2;             // one P buffer [128 x 64] bf16
-constexpr int kSmemBytes = kQBytes + kStages * kStageBytes + kPBytes + 256;    // 112.25 KB
-constexpr uint32_t kTmemCols = 256;              // S: 2 x 64, O: 128
+constexpr int kSmemBytes = kQBytes + kStages * kStageBytes + 256;              // 96.25 KB
+constexpr uint32_t kTmemCols = 256;              // S: 2 x 64 (P over the first 32 of each), O: 128
 constexpr uint32_t kSCol = 0, kOCol = 128;
 constexpr float kLazy = 8.f;                     // move the reference when the maximum grew by 2^8
 
@@ -51,9 +50,9 @@ struct Barriers {
   uint64_t q_full;
   uint64_t k_full[kStages], k_empty[kStages];     // keys: free again as soon as S_j is done
   uint64_t v_full[kStages], v_empty[kStages];     // values: free once P_j V_j is done
-  uint64_t s_full[2], s_free[2];
-  uint64_t p_full;       // the P tile is in shared memory (and stale value rows are zeroed)
-  uint64_t pv_done;      // P_j V_j has been added to O: P may be overwritten, O may be rescaled
+  uint64_t s_full[2];
+  uint64_t p_full;       // P_j lies in tensor memory over S_j (and stale value rows are zeroed)
+  uint64_t pv_done;      // P_j V_j has been added to O: O may be rescaled or read
   uint32_t tmem;
 };
 
@@ -102,8 +101,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap q_map,
   }
   uint8_t* q_s = smem;
   uint8_t* kv_s = q_s + kQBytes;
-  uint8_t* p_s = kv_s + kStages * kStageBytes;
-  Barriers* bar = reinterpret_cast<Barriers*>(p_s + kPBytes);
+  Barriers* bar = reinterpret_cast<Barriers*>(kv_s + kStages * kStageBytes);
 
   // blockIdx.x = head, blockIdx.y = tile: the tiles come heaviest first, so the blocks that
   // start first are the long ones of every head, and the short ones fill in behind them
@@ -125,10 +123,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap q_map,
       tma::mbar_init(&bar->v_full[s], 1);
       tma::mbar_init(&bar->v_empty[s], 1);
     }
-    for (int i = 0; i < 2; ++i) {
-      tma::mbar_init(&bar->s_full[i], 1);
-      tma::mbar_init(&bar->s_free[i], QT);
-    }
+    for (int i = 0; i < 2; ++i) tma::mbar_init(&bar->s_full[i], 1);
     tma::mbar_init(&bar->p_full, QT);
     tma::mbar_init(&bar->pv_done, 1);
     tma::fence_barrier_init();
@@ -182,11 +177,11 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap q_map,
         if (!tma::mbar_wait(&bar->p_full, i & 1, error, 403)) return false;
         if (!tma::mbar_wait(&bar->v_full[stage], (i / kStages) & 1, error, 412)) return false;
         tc::fence_after_sync();
-        const uint32_t p_addr = tma::smem_u32(p_s);
         const uint32_t v_addr = tma::smem_u32(kv_s + stage * kStageBytes + kTileBytes);
+        // A = P_i from tensor memory, where the softmax wrote it over the first half of S_i
 #pragma unroll
         for (int k = 0; k < KT / 16; ++k)
-          tc::mma_ss(tmem + kOCol, tc::smem_desc_k_major_sw128(p_addr + k * 32),
+          tc::mma_ts(tmem + kOCol, tmem + kSCol + (i & 1) * KT + k * 8,
                      smem_desc_mn_major_sw128(v_addr + k * 2048), idesc_pv, i > 0 || k > 0);
         tc::commit(&bar->pv_done);
         tc::commit(&bar->v_empty[stage]);
@@ -194,8 +189,9 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap q_map,
       };
       for (int j = 0; j < n && ok; ++j) {
         const int bj = j & 1, stage = j % kStages;
+        // (S_j goes where S_{j-2} and then P_{j-2} lay: P_{j-2} V_{j-2} was issued before
+        // this, and the tensor pipe runs one thread's products in the order it issued them)
         ok = tma::mbar_wait(&bar->k_full[stage], (j / kStages) & 1, error, 405);
-        if (ok && j >= 2) ok = tma::mbar_wait(&bar->s_free[bj], ((j >> 1) - 1) & 1, error, 406);
         if (!ok) break;
         tc::fence_after_sync();
         const uint32_t k_addr = tma::smem_u32(kv_s + stage * kStageBytes);
@@ -226,15 +222,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap q_map,
       if (!tma::mbar_wait(&bar->s_full[bj], (j >> 1) & 1, error, 407)) { ok = false; break; }
       tc::fence_after_sync();
       float s[KT];
-#pragma unroll
-      for (int c = 0; c < KT; c += 16) {
-        float v[16];
-        tc::ld_32x32b_x16(lane_base + kSCol + bj * KT + c, v);
-#pragma unroll
-        for (int i = 0; i < 16; ++i) s[c + i] = v[i];
-      }
-      tc::fence_before_sync();
-      tma::mbar_arrive(&bar->s_free[bj]);
+      tc::ld_32x32b_x64(lane_base + kSCol + bj * KT, s);
       const int key0 = (t0 + j) * KT;
       const bool needs_mask = key0 + KT - 1 > pos0 || (window > 0 && key0 < last_pos - window + 1);
       if (needs_mask) {
@@ -255,12 +243,14 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap q_map,
       }
       const float big = fmaxf(fmaxf(big4[0], big4[1]), fmaxf(big4[2], big4[3]));
       m_true = fmaxf(m_true, big * scale_log2e);
-      // P_{j-1} V_{j-1} must be done before P is overwritten and before O is touched
-      if (j >= 1 && !tma::mbar_wait(&bar->pv_done, (j - 1) & 1, error, 408)) { ok = false; break; }
+      bool waited = j == 0;          // whether P_{j-1} V_{j-1} is known to be done
       const bool move = m_true > m_ref + kLazy;      // (also true the first time a key is seen)
       if (__any_sync(0xffffffffu, move)) {
         const float factor = move ? mma::exp2_fast(m_ref - m_true) : 1.f;   // 0 when m_ref = -inf
         if (j >= 1) {
+          // O is touched: P_{j-1} V_{j-1} must be done
+          if (!tma::mbar_wait(&bar->pv_done, (j - 1) & 1, error, 408)) { ok = false; break; }
+          waited = true;
           tc::fence_after_sync();
 #pragma unroll
           for (int c = 0; c < D; c += 16) {
@@ -278,25 +268,20 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap q_map,
         }
       }
       const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
-      // P row, bf16, into the swizzled K-major layout of an A operand: 8 chunks of 8 keys.
-      // Exponents two at a time (one fma for both), four running sums.
+      // P row, bf16 pairs, into tensor memory over the first half of this row of S_j: the A
+      // operand of P.V. Exponents two at a time (one fma for both), four running sums.
       float sum4[4] = {0.f, 0.f, 0.f, 0.f};
-      uint8_t* p_row = p_s + r * 128;
+      uint32_t packed[KT / 2];
       const float minus_m = -m_use;
 #pragma unroll
-      for (int ch = 0; ch < KT / 8; ++ch) {
-        uint32_t packed[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          float e0, e1;
-          mma::fma2(e0, e1, s[ch * 8 + 2 * i], s[ch * 8 + 2 * i + 1], scale_log2e, minus_m);
-          const float p0 = mma::exp2_fast(e0), p1 = mma::exp2_fast(e1);
-          mma::add2(sum4[(i & 1) * 2], sum4[(i & 1) * 2 + 1], p0, p1);
-          packed[i] = mma::pack_bf16(p0, p1);
-        }
-        *reinterpret_cast<uint4*>(p_row + ((ch ^ (r & 7)) << 4)) =
-            make_uint4(packed[0], packed[1], packed[2], packed[3]);
+      for (int i = 0; i < KT / 2; ++i) {
+        float e0, e1;
+        mma::fma2(e0, e1, s[2 * i], s[2 * i + 1], scale_log2e, minus_m);
+        const float p0 = mma::exp2_fast(e0), p1 = mma::exp2_fast(e1);
+        mma::add2(sum4[(i & 1) * 2], sum4[(i & 1) * 2 + 1], p0, p1);
+        packed[i] = mma::pack_bf16(p0, p1);
       }
+      tc::st_32x32b_x32(lane_base + kSCol + bj * KT, packed);
       const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
       l += sum;
       // the sequence's last block: value rows past its end are stale; zero them before P.V
@@ -310,8 +295,11 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap q_map,
         for (int row = valid + (r >> 4); row < KT; row += QT / 16)
           *reinterpret_cast<uint4*>(vt + ((r & 15) >> 3) * (KT * 128) + row * 128 + ((r & 7) << 4)) =
               make_uint4(0, 0, 0, 0);
+        tma::fence_proxy_async();
       }
-      tma::fence_proxy_async();
+      // every product is waited for once, in order (the barrier's phases are told apart by
+      // one bit); here it has long been done
+      if (!waited && !tma::mbar_wait(&bar->pv_done, (j - 1) & 1, error, 408)) { ok = false; break; }
       tc::fence_before_sync();
       tma::mbar_arrive(&bar->p_full);
     }
