@@ -386,28 +386,36 @@ def main() -> int:
         return slots
 
     def decode_run(batch: int, steps: int, warmup: int):
+        """`steps` decode steps of `batch` sequences, greedy. Each step takes its tokens
+        where the step before left them on the device (as `Engine.generate` does), and
+        every step's tokens are copied to pinned host memory; the host reads them at the
+        end."""
         slots = filled(batch)
-        tokens = [rng.integers(0, cfg.vocab_size, 1) for _ in slots]
+        chosen = torch.as_tensor(rng.integers(0, cfg.vocab_size, batch), dtype=torch.int32).cuda()
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        read = []
 
-        def one():
-            logits = engine.step(slots, tokens)
-            chosen = sampling.choose(logits, greedy).cpu().numpy()
-            return [chosen[i:i + 1] for i in range(batch)]
+        def one(chosen):
+            chosen = sampling.choose(engine.step(slots, device_tokens=chosen), greedy)
+            host = torch.empty((batch,), dtype=torch.int32, pin_memory=True)
+            host.copy_(chosen, non_blocking=True)
+            read.append(host)
+            return chosen
 
         for _ in range(warmup):
-            tokens = one()
+            chosen = one(chosen)
         torch.cuda.synchronize()
         launches0 = _lib.launches
         sampler = ClockSampler()
         sampler.start()
         start.record()
         for _ in range(steps):
-            tokens = one()
+            chosen = one(chosen)
         stop.record()
         torch.cuda.synchronize()
         clocks = sampler.stop()
         ms = start.elapsed_time(stop)
+        assert all(0 <= int(t) < cfg.vocab_size for host in read for t in host.tolist())
         engine.close(slots)
         return ms, _lib.launches - launches0, clocks
 

@@ -20,7 +20,7 @@ from .. import sampling
 from ..ops import _lib
 from ..cache import BLOCK, CacheFull, SequenceCache
 from ..config import config_from_dict, config_from_folder
-from .generate import (COMPLETE, DECODING, EXHAUSTED, PREFILLING, Ending, RequestState,
+from .generate import (decode_ahead, COMPLETE, DECODING, EXHAUSTED, PREFILLING, Ending, RequestState,
                        check_prompt, check_window, plan_batches, plan_prefill, positions_needed)
 from .model import DecoderModel
 from .step import StepStager
@@ -137,13 +137,25 @@ class Engine:
         """End sequences; what they hold goes back to the cache."""
         self._need_cache().close(slots)
 
-    def step(self, slots: list, new_tokens: list, want: list | None = None) -> torch.Tensor:
+    def step(self, slots: list, new_tokens: list | None = None, want: list | None = None, *,
+             device_tokens: torch.Tensor | None = None) -> torch.Tensor:
         """Feed `new_tokens[i]` to the sequence in `slots[i]`, after what its cache
         already holds, all sequences as one batch. Returns fp32 logits
         [wanted, vocab] on the device for `want[i]`, the places among
         `new_tokens[i]` whose logits are asked for, in the order of the sequences
-        (default: each sequence's last token)."""
+        (default: each sequence's last token).
+
+        `device_tokens` (int32 [len(slots)], on the device) instead of `new_tokens`: one
+        token for each sequence, taken from the device on the stream, so that a step can be
+        launched before the host has read the tokens the step before it chose."""
         cache = self._need_cache()
+        if device_tokens is not None:
+            if new_tokens is not None:
+                raise ValueError("give new_tokens or device_tokens, not both")
+            if device_tokens.dtype != torch.int32 or device_tokens.shape != (len(slots),) \
+                    or not device_tokens.is_cuda:
+                raise ValueError("device_tokens: int32 [len(slots)] on the engine's device")
+            new_tokens = [(0,)] * len(slots)
         if len(slots) != len(new_tokens) or not slots:
             raise ValueError("step needs as many token lists as slots, and at least one")
         if len(set(slots)) != len(slots):
@@ -164,7 +176,8 @@ class Engine:
             base += c
         with torch.cuda.device(self.device):
             cache.reserve(slots, ends)
-            ctx = self._stager.build(slots, new_tokens, starts, rows, cache.tables_for(slots))
+            ctx = self._stager.build(slots, new_tokens, starts, rows, cache.tables_for(slots),
+                                     device_tokens)
             if self.cuda_graphs and self.model.graph_safe and ctx.is_decode \
                     and rows == list(range(len(slots))):
                 logits = self._decode_by_graph(ctx, cache)
@@ -292,58 +305,91 @@ class Engine:
         slot_of = {r.index: s for r, s in zip(requests, slots)}
         live = list(requests)
 
+        def positions(r):           # what its cache holds: the last new token is never fed
+            return len(r.prompt) + len(r.out) - 1
+
         def finish(r, state=COMPLETE, reason=None):
-            endings[r.index] = Ending(state, int(cache.lengths[slot_of[r.index]]),
-                                      np.asarray(r.out, np.int32), reason or r.reason)
+            endings[r.index] = Ending(state, positions(r), np.asarray(r.out, np.int32),
+                                      reason or r.reason)
             cache.close([slot_of[r.index]])
 
         try:
             # prefill: every prompt whole, in one step unless the batch is too large
-            plans = plan_prefill([len(r.prompt) for r in requests], self.max_step_tokens)
-            logits = {}
-            for plan in plans:
-                step_slots = [slots[i] for i, _, _ in plan]
-                tokens = [requests[i].prompt[a:a + n] for i, a, n in plan]
-                ends = [a + n == len(requests[i].prompt) for i, a, n in plan]
-                want = [[n - 1] if last else [] for (_, _, n), last in zip(plan, ends)]
-                out = self.step(step_slots, tokens, want)
-                row = 0
-                for (i, _, _), last in zip(plan, ends):
-                    if last:
-                        logits[i] = out[row]
-                        row += 1
-            first = torch.stack([logits[i] for i in range(len(requests))])
-            chosen = self._choose(first, params, live)
-            for r, token in zip(live, chosen):
+            try:
+                plans = plan_prefill([len(r.prompt) for r in requests], self.max_step_tokens)
+                logits = {}
+                for plan in plans:
+                    step_slots = [slots[i] for i, _, _ in plan]
+                    tokens = [requests[i].prompt[a:a + n] for i, a, n in plan]
+                    ends = [a + n == len(requests[i].prompt) for i, a, n in plan]
+                    want = [[n - 1] if last else [] for (_, _, n), last in zip(plan, ends)]
+                    out = self.step(step_slots, tokens, want)
+                    row = 0
+                    for (i, _, _), last in zip(plan, ends):
+                        if last:
+                            logits[i] = out[row]
+                            row += 1
+            except CacheFull as exc:
+                for r in live:
+                    endings[r.index] = Ending(EXHAUSTED, int(cache.lengths[slot_of[r.index]]),
+                                              np.asarray(r.out, np.int32), str(exc))
+                    cache.close([slot_of[r.index]])
+                return
+            first = self._choose(torch.stack([logits[i] for i in range(len(requests))]),
+                                 params, live)
+            for r, token in zip(live, self._read(first)):
+                r.drawn = 1
                 tell(PREFILLING, len(r.prompt), None, r.index)
                 r.accept(token, stops, max_new_tokens)
             for r in [r for r in live if r.finished]:
                 finish(r)
-            live = [r for r in live if not r.finished]
-            # decode: one token for each live request a step
-            while live:
-                out = self.step([slot_of[r.index] for r in live],
-                                [np.asarray(r.out[-1:], np.int32) for r in live])
-                chosen = self._choose(out, params, live)
-                for r, token in zip(live, chosen):
-                    r.accept(token, stops, max_new_tokens)
-                    tell(DECODING, int(cache.lengths[slot_of[r.index]]), int(token), r.index)
-                for r in [r for r in live if r.finished]:
-                    finish(r)
-                live = [r for r in live if not r.finished]
-        except CacheFull as exc:
-            for r in live:
-                finish(r, EXHAUSTED, str(exc))
+            keep = [j for j, r in enumerate(live) if not r.finished]
+            live = [live[j] for j in keep]
+            if len(keep) < len(requests):
+                first = _Chosen(first.tokens[torch.as_tensor(keep, dtype=torch.long, device=self.device)], None, None)
+
+            # decode: one token for each live request a step, a step ahead of the host
+            def launch(step_requests, feed, rows):
+                tokens = feed.tokens
+                if len(rows) != tokens.shape[0]:
+                    tokens = tokens[torch.as_tensor(rows, dtype=torch.long, device=self.device)]
+                out = self.step([slot_of[r.index] for r in step_requests], device_tokens=tokens)
+                return self._choose(out, params, step_requests)
+
+            decode_ahead(live, first, max_new_tokens, stops, launch, self._read,
+                         on_token=lambda r, t: tell(DECODING, positions(r), int(t), r.index),
+                         on_finish=finish,
+                         on_exhausted=lambda r, why: finish(r, EXHAUSTED, why))
         except BaseException:
             held = [slot_of[r.index] for r in requests if r.index not in endings]
             cache.close(held)
             raise
 
-    def _choose(self, logits, params, live) -> list[int]:
+    def _choose(self, logits, params, live) -> "_Chosen":
+        """A token for each row of `logits`, chosen on the device; its copy to the host is
+        on its way (pinned memory) but nothing waits for it here."""
         tokens = sampling.choose(logits, params, [r.index for r in live],
-                                 [len(r.out) for r in live]).cpu().tolist()
+                                 [r.drawn for r in live])
+        host = torch.empty(tokens.shape, dtype=torch.int32, pin_memory=True)
+        host.copy_(tokens, non_blocking=True)
+        done = torch.cuda.Event()
+        done.record()
+        return _Chosen(tokens, host, done)
+
+    def _read(self, chosen: "_Chosen") -> list[int]:
+        chosen.done.synchronize()
+        tokens = chosen.host.tolist()
         sampling.check_chosen(tokens, self.spec.vocab_size)
         return tokens
+
+
+class _Chosen:
+    """The tokens a step chose: on the device, and on their way to the host."""
+
+    __slots__ = ("tokens", "host", "done")
+
+    def __init__(self, tokens, host, done):
+        self.tokens, self.host, self.done = tokens, host, done
 
 
 def _is_list_of_sequences(prompt) -> bool:

@@ -16,6 +16,7 @@ from dataclasses import dataclass, field
 import numpy as np
 
 from ..cache import BLOCK
+from ..cache.allocator import CacheFull
 
 PREFILLING, DECODING = "prefilling", "decoding"
 COMPLETE, EXHAUSTED = "complete", "exhausted"
@@ -94,6 +95,7 @@ class RequestState:
     prompt: np.ndarray
     out: list = field(default_factory=list)
     reason: str = ""                 # '' while running
+    drawn: int = 0                   # tokens chosen for it so far, read back by the host or not
 
     @property
     def finished(self) -> bool:
@@ -106,6 +108,60 @@ class RequestState:
             self.reason = "stop"
         elif len(self.out) >= max_new_tokens:
             self.reason = "length"
+
+
+def decode_ahead(live: list, first_feed, max_new_tokens: int, stop_ids, launch, read,
+                 on_token=None, on_finish=None, on_exhausted=None) -> None:
+    """The decode loop of one batch, one step ahead of the tokens the host has read.
+
+    `live`: requests whose first token (from the prefill) has been accepted and that go
+    on; `first_feed`: whatever `launch` needs to find those first tokens (row i belongs to
+    live[i]). `launch(requests, feed, rows)` starts a step in which requests[j] is fed row
+    rows[j] of the tokens of `feed` (the first feed, or what the launch before returned)
+    and a token is chosen for each; it returns at once with a handle, or raises
+    `CacheFull`. `read(handle)` waits for those tokens and returns them as ints.
+
+    Step t + 1 is launched BEFORE the tokens of step t are read: its inputs are taken
+    where step t left them, so the host's work overlaps the device's. Who runs in step
+    t + 1 is decided without them: everyone of step t but the requests whose count is
+    complete. A request that turns out to have ended at a stop token in step t has then
+    run one step too many; that step's token for it is thrown away. `on_token(request,
+    token)` and `on_finish(request)` are called as tokens are read, in order;
+    `on_exhausted(request, message)` for those a full cache cuts short.
+    """
+    def settle(step):
+        requests, handle = step
+        for r, token in zip(requests, read(handle)):
+            if r.finished:
+                continue                      # it ended a step earlier: this one was run in vain
+            r.accept(token, stop_ids, max_new_tokens)
+            if on_token:
+                on_token(r, token)
+            if r.finished and on_finish:
+                on_finish(r)
+
+    in_flight = None
+    feed, rows = first_feed, list(range(len(live)))
+    while live:
+        try:
+            handle = launch(live, feed, rows)
+        except CacheFull as exc:
+            if in_flight is not None:
+                settle(in_flight)
+                in_flight = None
+            for r in live:
+                if not r.finished and on_exhausted:
+                    on_exhausted(r, str(exc))
+            return
+        for r in live:
+            r.drawn += 1
+        if in_flight is not None:
+            settle(in_flight)
+        in_flight = (live, handle)
+        after = [j for j, r in enumerate(live) if r.drawn < max_new_tokens and not r.finished]
+        feed, rows, live = handle, after, [live[j] for j in after]
+    if in_flight is not None:
+        settle(in_flight)
 
 
 def check_prompt(ids, vocab_size: int, what: str = "token_ids") -> np.ndarray:

@@ -48,13 +48,17 @@ class StepContext:
 
 
 class StepStager:
-    """Pinned host buffer and device buffer that carry a step's integers."""
+    """Pinned host buffers and the device buffer that carry a step's integers. There are two
+    host buffers, used in turn: a step can be written while the copy of the step before it
+    is still on its way (a decode loop that runs ahead of the tokens it has read back)."""
 
     def __init__(self, device):
         self.device = torch.device(device)
         self.capacity = 0
-        self.host = self.dev = None
-        self.copied = None
+        self.hosts = [None, None]
+        self.dev = None
+        self.copied = [None, None]
+        self.turn = 0
         self.last_bytes = 0
         self.generation = 0
 
@@ -63,13 +67,17 @@ class StepStager:
             return
         self.capacity = max(1 << 18, 2 * count)
         self.generation += 1                 # device addresses change: captured graphs are stale
-        self.host = torch.empty(self.capacity, dtype=torch.int32, pin_memory=True)
+        self.hosts = [torch.empty(self.capacity, dtype=torch.int32, pin_memory=True)
+                      for _ in range(2)]
         self.dev = torch.empty(self.capacity, dtype=torch.int32, device=self.device)
-        self.copied = None
+        self.copied = [None, None]
 
-    def build(self, slots: list, new_tokens: list, starts: list, want_rows, tables: list) -> StepContext:
+    def build(self, slots: list, new_tokens: list, starts: list, want_rows, tables: list,
+              device_tokens: torch.Tensor | None = None) -> StepContext:
         """`new_tokens[i]`: the tokens sequence i brings; `starts[i]`: its length
-        before the step; `want_rows`: flat token rows whose logits are wanted;
+        before the step; with `device_tokens` (int32 [B] on the device, one token a sequence)
+        the ids are taken from there, on the stream, and `new_tokens` gives the counts only;
+        `want_rows`: flat token rows whose logits are wanted;
         `tables[g]`: numpy int32 [B, max_blocks] of cache group g."""
         B = len(slots)
         counts = [len(t) for t in new_tokens]
@@ -97,9 +105,10 @@ class StepStager:
             offsets[name] = total
             total += -(-max(n, 1) // 4) * 4          # 16-byte aligned fields
         self._ensure(total)
-        if self.copied is not None:
-            self.copied.synchronize()               # the last copy has left the host buffer
-        host = self.host.numpy()
+        turn = self.turn = 1 - self.turn
+        if self.copied[turn] is not None:
+            self.copied[turn].synchronize()         # its last copy has left this host buffer
+        host = self.hosts[turn].numpy()
 
         def put(name, values):
             values = np.asarray(values, dtype=np.int32).reshape(-1)
@@ -107,8 +116,9 @@ class StepStager:
 
         cu = np.zeros(B + 1, dtype=np.int64)
         np.cumsum(counts, out=cu[1:])
-        put("token_ids", np.concatenate([np.asarray(t, dtype=np.int64) for t in new_tokens])
-            if T else np.zeros(0))
+        put("token_ids", np.zeros(T) if device_tokens is not None else
+            np.concatenate([np.asarray(t, dtype=np.int64) for t in new_tokens]) if T
+            else np.zeros(0))
         put("positions", np.concatenate([np.arange(s, s + c) for s, c in zip(starts, counts)])
             if T else np.zeros(0))
         put("token_seq", np.repeat(np.arange(B), counts))
@@ -120,9 +130,11 @@ class StepStager:
         for g, t in enumerate(tables):
             put(f"table{g}", t)
         self.last_bytes = 4 * total
-        self.dev[:total].copy_(self.host[:total], non_blocking=True)
-        self.copied = torch.cuda.Event()
-        self.copied.record()
+        self.dev[:total].copy_(self.hosts[turn][:total], non_blocking=True)
+        self.copied[turn] = torch.cuda.Event()
+        self.copied[turn].record()
+        if device_tokens is not None:
+            self.dev[offsets["token_ids"]:offsets["token_ids"] + T].copy_(device_tokens)
 
         def view(name, n):
             return self.dev[offsets[name]:offsets[name] + n]

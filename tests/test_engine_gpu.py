@@ -175,6 +175,21 @@ def test_greedy_generation_through_the_entry_point(engines, model_folders):
         assert e.reason == ("stop" if stop in w else "length")
     assert engine.generate(prompts[0], 0).size == 0
     assert engine.cache.slots.held == 0
+    # the loop runs a step ahead of the tokens it has read: short counts, and a stop token at
+    # every place of every request, end where the plain loop ends
+    for n in (1, 2, 3):
+        got = engine.generate([p.tolist() for p in prompts], n, stop_at_eos=False)
+        assert [g.tolist() for g in got] == [w[:n] for w in want]
+    for place in range(8):
+        for who in range(len(prompts)):
+            stop = want[who][place]
+            got = engine.generate([p.tolist() for p in prompts], 8, stop_token_ids=[stop])
+            for g, w, e in zip(got, want, engine.endings):
+                cut = w.index(stop) + 1 if stop in w else len(w)
+                assert g.tolist() == w[:cut] and e.positions == len(g) + e.positions - len(g)
+                assert e.reason == ("stop" if stop in w else "length")
+            assert engine.endings[who].positions == len(prompts[who]) + len(got[who]) - 1
+    assert engine.cache.slots.held == 0
 
 
 def test_temperature_generation_matches_the_plain_sampler(engines, model_folders):

@@ -67,3 +67,90 @@ def test_prompt_checks():
     with pytest.raises(ValueError, match="context window"):
         check_window(129, 128)
     check_window(128, 128)
+
+
+# ---- the decode loop that runs a step ahead of the tokens it has read -------------------------
+
+def _fake_model(request, step):
+    """The token request `request` draws as its `step`-th (a fixed function of both)."""
+    return (request * 7 + step * 3) % 11
+
+
+def _run_ahead(prompts, max_new, stops, full_at=None):
+    """decode_ahead over a fake device that remembers what was launched."""
+    from semantic_aware_adaptive_kv_cache_precision_b200.cache.allocator import CacheFull
+    from semantic_aware_adaptive_kv_cache_precision_b200.engine.generate import (
+        RequestState, decode_ahead)
+    requests = [RequestState(i, np.zeros(n, np.int32)) for i, n in enumerate(prompts)]
+    log = {"launches": [], "unread_at_launch": [], "finished": [], "exhausted": []}
+    live = []
+    for r in requests:
+        r.drawn = 1
+        r.accept(_fake_model(r.index, 0), stops, max_new)
+        if r.finished:
+            log["finished"].append(r.index)
+        else:
+            live.append(r)
+    first = [r.out[0] for r in live]
+    unread = {"n": 0}
+
+    def launch(step_requests, feed, rows):
+        if full_at is not None and len(log["launches"]) == full_at:
+            raise CacheFull("no block left")
+        # the tokens fed are those the step before chose for the same requests
+        fed = [feed[j] for j in rows]
+        for r, t in zip(step_requests, fed):
+            assert t == _fake_model(r.index, r.drawn - 1), "a request was fed another's token"
+        log["launches"].append([r.index for r in step_requests])
+        log["unread_at_launch"].append(unread["n"])
+        unread["n"] += 1
+        return [_fake_model(r.index, r.drawn) for r in step_requests]
+
+    def read(handle):
+        unread["n"] -= 1
+        return list(handle)
+
+    decode_ahead(live, first, max_new, stops, launch, read,
+                 on_finish=lambda r: log["finished"].append(r.index),
+                 on_exhausted=lambda r, why: log["exhausted"].append((r.index, why)))
+    return requests, log
+
+
+def _plain_loop(prompts, max_new, stops):
+    out = []
+    for i in range(len(prompts)):
+        tokens = []
+        while True:
+            tokens.append(_fake_model(i, len(tokens)))
+            if tokens[-1] in stops or len(tokens) >= max_new:
+                break
+        out.append(tokens)
+    return out
+
+
+@pytest.mark.parametrize("max_new", [1, 2, 3, 9])
+@pytest.mark.parametrize("stops", [frozenset(), frozenset({4}), frozenset({0, 6})])
+def test_running_a_step_ahead_gives_the_same_tokens(max_new, stops):
+    prompts = [3, 5, 2, 8, 1]
+    requests, log = _run_ahead(prompts, max_new, stops)
+    assert [r.out for r in requests] == _plain_loop(prompts, max_new, stops)
+    assert sorted(log["finished"]) == list(range(len(prompts))) and not log["exhausted"]
+    # every launch but the first is made with exactly one step unread: the loop is one ahead
+    assert log["unread_at_launch"] == ([0] + [1] * (len(log["launches"]) - 1))[:len(log["launches"])]
+    for r in requests:
+        steps_run = sum(r.index in step for step in log["launches"])
+        needed = len(r.out) - 1
+        # a request whose count was complete is never run again; one that met a stop token
+        # runs at most one step too many
+        assert steps_run == needed or (r.reason == "stop" and steps_run == needed + 1)
+        if r.reason == "length":
+            assert steps_run == needed
+
+
+def test_a_full_cache_ends_what_is_left_after_reading_what_was_in_flight():
+    requests, log = _run_ahead([3, 4, 5], max_new=8, stops=frozenset(), full_at=2)
+    # two steps ran, their tokens were read (three tokens each with the prefill's), then the
+    # third launch found the cache full
+    assert [len(r.out) for r in requests] == [3, 3, 3]
+    assert [i for i, _ in log["exhausted"]] == [0, 1, 2]
+    assert all("no block" in why for _, why in log["exhausted"])
