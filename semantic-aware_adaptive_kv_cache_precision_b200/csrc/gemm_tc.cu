@@ -25,6 +25,7 @@
 // this (`src/core_kernels/linear.cu:85-142`); warps: 0 = TMA, 1 = MMA issue and tensor
 // memory, 2..5 = epilogue. TMA loads are plain per-block loads, never cluster multicast.
 #include "common.cuh"
+#include "mma.cuh"
 #include "tcgen05.cuh"
 #include "tma.cuh"
 
@@ -159,6 +160,95 @@ __device__ __forceinline__ void reduce_columns(const Params& p, uint32_t base, i
         if (kDual) up += part_up[j][s];
       }
       finish<kEpi>(p, k_part, m0 + c, n, acc, up, bias);
+    }
+  }
+}
+
+__device__ __forceinline__ float4 ld_peer4(uint32_t local, uint32_t rank) {
+  uint32_t remote;
+  float4 v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(rank));
+  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "r"(remote)
+               : "memory");
+  return v;
+}
+
+// Four consecutive weight rows n .. n + 3 of one token column m, finished together.
+template <int kEpi>
+__device__ __forceinline__ void finish4(const Params& p, int part, int m, int n, float4 c,
+                                        float4 up, float4 bias) {
+  if (m >= p.M || n >= p.N) return;
+  const long long at = (long long)m * p.ldo + n + part * p.part_stride;
+  const bool whole = n + 3 < p.N && (p.ldo & 3) == 0 && (p.part_stride & 3) == 0;
+  if (kEpi == EPI_ACCUM || !whole) {
+    finish<kEpi>(p, part, m, n, c.x, up.x, bias.x);
+    finish<kEpi>(p, part, m, n + 1, c.y, up.y, bias.y);
+    finish<kEpi>(p, part, m, n + 2, c.z, up.z, bias.z);
+    finish<kEpi>(p, part, m, n + 3, c.w, up.w, bias.w);
+  } else if (kEpi == EPI_F32) {
+    *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + at) =
+        make_float4(c.x + bias.x, c.y + bias.y, c.z + bias.z, c.w + bias.w);
+  } else {
+    float r[4] = {c.x + bias.x, c.y + bias.y, c.z + bias.z, c.w + bias.w};
+    if (kEpi == EPI_GATED) {
+      const float g[4] = {c.x, c.y, c.z, c.w}, u[4] = {up.x, up.y, up.z, up.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) r[i] = g[i] / (1.0f + expf(-g[i])) * u[i];
+    }
+    *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(p.out) + at) =
+        make_uint2(mma::pack_bf16(r[0], r[1]), mma::pack_bf16(r[2], r[3]));
+  }
+}
+
+// The same reduction for token tiles of 32 and more with a cluster of 2, 4 or 8, where the
+// remote reads are many (at 64 tokens the scheme above spent 5.6 us of the gate/up product's
+// 14.5 us in them). A thread no longer keeps to its own row: the 32 lanes of a warp take the
+// 128 rows of ONE token column four rows each, so that a warp's remote read is 512
+// contiguous bytes, and the four warps take four columns at a time; results leave as 8- or
+// 16-byte stores of four rows. (Partials laid out row by row, so that a thread could read
+// four of ITS columns at once, were slower: a warp's read was then 32 scattered pieces.)
+template <int MT, int kEpi, int S>
+__device__ __forceinline__ void reduce_quads(const Params& p, uint32_t base, int rank, int k_part,
+                                             int m0, int n0) {
+  constexpr bool kDual = kEpi == EPI_GATED;
+  const int t = threadIdx.x - 64;                 // 0..127 among the epilogue threads
+  const int r0 = (t & 31) * 4;                    // this thread's four rows
+  const int n = n0 + r0;
+  float4 bias = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (k_part == 0)
+    bias = make_float4(bias_at(p, n), bias_at(p, n + 1), bias_at(p, n + 2), bias_at(p, n + 3));
+  const int live = min(MT, p.M - m0);
+  // as many columns a round as keep about sixteen 16-byte reads of a thread in flight
+  constexpr int kAccs = kDual ? 2 : 1;
+  constexpr int kIter = 16 / (S * kAccs) > 0 ? 16 / (S * kAccs) : 1;
+#pragma unroll 1
+  for (int c0 = rank + (t >> 5) * S; c0 < live; c0 += 4 * S * kIter) {
+    float4 g[kIter][S], u[kDual ? kIter : 1][S];
+#pragma unroll
+    for (int k = 0; k < kIter; ++k) {
+      const int c = c0 + k * 4 * S;
+#pragma unroll
+      for (int s = 0; s < S; ++s) {
+        const bool on = c < live;
+        g[k][s] = on ? ld_peer4(base + (c * BM + r0) * 4, s) : make_float4(0.f, 0.f, 0.f, 0.f);
+        if (kDual)
+          u[k][s] = on ? ld_peer4(base + ((MT + c) * BM + r0) * 4, s)
+                       : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < kIter; ++k) {
+      const int c = c0 + k * 4 * S;
+      if (c >= live) break;
+      float4 acc = g[k][0], up = kDual ? u[k][0] : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int s = 1; s < S; ++s) {
+        acc.x += g[k][s].x; acc.y += g[k][s].y; acc.z += g[k][s].z; acc.w += g[k][s].w;
+        if (kDual) { up.x += u[k][s].x; up.y += u[k][s].y; up.z += u[k][s].z; up.w += u[k][s].w; }
+      }
+      finish4<kEpi>(p, k_part, m0 + c, n, acc, up, bias);
     }
   }
 }
@@ -313,7 +403,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
       const float bias = k_part == 0 ? bias_at(p, n) : 0.f;
       const uint32_t base = tma::smem_u32(smem);
       // token columns split, split + splits, ... are finished by this block
-      if (p.splits == 2)
+      if (MT >= 32 && p.splits == 2)
+        reduce_quads<MT, kEpi, 2>(p, base, split, k_part, m0, n0);
+      else if (MT >= 32 && p.splits == 4)
+        reduce_quads<MT, kEpi, 4>(p, base, split, k_part, m0, n0);
+      else if (MT >= 32 && p.splits == 8)
+        reduce_quads<MT, kEpi, 8>(p, base, split, k_part, m0, n0);
+      else if (p.splits == 2)
         reduce_columns<MT, kEpi, 2>(p, base, split, k_part, m0, n, row, bias);
       else if (p.splits == 4)
         reduce_columns<MT, kEpi, 4>(p, base, split, k_part, m0, n, row, bias);
