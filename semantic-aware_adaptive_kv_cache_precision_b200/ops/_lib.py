@@ -90,7 +90,15 @@ def ptr(t):
     return None if t is None else t.data_ptr()
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def stream() -> int:
+    """The current stream of the current device, as the integer the kernels take. (The raw
+    getter costs a fraction of a microsecond; `torch.cuda.current_stream()` builds a Python
+    object on every call, 15 us that a prefill step pays 150 times.)"""
+    if _raw_stream is not None:
+        return _raw_stream(torch.cuda.current_device())
     return torch.cuda.current_stream().cuda_stream
 
 
