@@ -72,6 +72,11 @@ class Engine:
         self._graph_pool = None
         self._decode_ran_eagerly = False
         self.graph_failure = None
+        self._prefill_graphs = {}
+        #: steps of up to this many tokens are captured when their shape repeats (0: never);
+        #: at most `prefill_graph_count` of them are kept
+        self.prefill_graph_tokens = 8192
+        self.prefill_graph_count = 8
         self.ending = None
         self.endings: list = []
         self._loaded = False
@@ -181,6 +186,10 @@ class Engine:
             if self.cuda_graphs and self.model.graph_safe and ctx.is_decode \
                     and rows == list(range(len(slots))):
                 logits = self._decode_by_graph(ctx, cache)
+            elif self.cuda_graphs and self.model.graph_safe and 0 < len(rows) <= 64 \
+                    and ctx.tokens <= self.prefill_graph_tokens:
+                logits = self._prefill_by_graph(ctx, cache, (tuple(counts), tuple(starts),
+                                                             tuple(rows)))
             else:
                 x = self.model.hidden(ctx, cache)
                 logits = self.model.logits(x, ctx.want) if rows else torch.empty(
@@ -226,6 +235,51 @@ class Engine:
             _lib.launches = before
         entry[0].replay()
         _lib.launches += entry[2]            # the kernels of this library inside the graph
+        return entry[1].clone()
+
+    def _prefill_by_graph(self, ctx, cache, shape) -> torch.Tensor:
+        """A step that is not a decode step, through a CUDA graph once its shape (how many
+        tokens each sequence brings, after how many, and which logits are wanted) has come
+        up before: the first time it runs kernel by kernel, the second time it is captured,
+        from then on replayed. Launching a prefill's 400 kernels from Python takes 4 to 5 ms,
+        longer than a short prompt's kernels run; a replay takes what the kernels take.
+        Requests of a shape never seen again cost nothing but a dictionary entry."""
+        key = (shape, tuple(tuple(t.shape) for t in ctx.tables), self._stager.generation)
+        entry = self._prefill_graphs.get(key)
+        if entry is None:                                   # first time: eagerly
+            if len(self._prefill_graphs) >= 256:
+                self._prefill_graphs.clear()
+            out = self.model.logits(self.model.hidden(ctx, cache), ctx.want)
+            self._prefill_graphs[key] = ctx.plans          # what the parts worked out for it
+            return out
+        if isinstance(entry, dict):                         # second time: capture
+            captured = sum(1 for e in self._prefill_graphs.values() if isinstance(e, tuple))
+            if captured >= self.prefill_graph_count:
+                ctx.plans = entry
+                return self.model.logits(self.model.hidden(ctx, cache), ctx.want)
+            ctx.plans = entry                               # nothing is uploaded while capturing
+            graph = torch.cuda.CUDAGraph()
+            if self._graph_pool is None:
+                self._graph_pool = torch.cuda.graph_pool_handle()
+            torch.cuda.synchronize(self.device)
+            before = _lib.launches
+            try:
+                with torch.cuda.graph(graph, pool=self._graph_pool):
+                    out = self.model.logits(self.model.hidden(ctx, cache), ctx.want)
+            except Exception as exc:
+                self.graph_failure = repr(exc)
+                self.prefill_graph_tokens = 0               # no more attempts
+                _lib.launches = before
+                try:
+                    torch.cuda.synchronize(self.device)
+                except Exception:
+                    pass
+                return self.model.logits(self.model.hidden(ctx, cache), ctx.want)
+            entry = (graph, out, _lib.launches - before, entry)
+            self._prefill_graphs[key] = entry
+            _lib.launches = before
+        entry[0].replay()
+        _lib.launches += entry[2]
         return entry[1].clone()
 
     # -- whole sequences ---------------------------------------------------------------

@@ -186,10 +186,14 @@ def attention_prefill_tc(qkv: torch.Tensor, k_cache: torch.Tensor, v_cache: torc
     n_folds = 0 if folds is None else folds.shape[0]
     if n_folds:
         need = partials * heads * 128 * (head_dim + 2)
-        scratch = _wide_scratch.get(qkv.device)
-        if scratch is None or scratch.numel() < need:
-            scratch = torch.empty(max(need, 1 << 22), dtype=torch.float32, device=qkv.device)
-            _wide_scratch[qkv.device] = scratch
+        if torch.cuda.is_current_stream_capturing():
+            # a graph keeps what it was captured with: scratch of its own, from its pool
+            scratch = torch.empty(need, dtype=torch.float32, device=qkv.device)
+        else:
+            scratch = _wide_scratch.get(qkv.device)
+            if scratch is None or scratch.numel() < need:
+                scratch = torch.empty(max(need, 1 << 22), dtype=torch.float32, device=qkv.device)
+                _wide_scratch[qkv.device] = scratch
         part_o = scratch[:partials * heads * 128 * head_dim]
         part_ml = scratch[partials * heads * 128 * head_dim:need]
     call("sakv_prefill_attention_tc", q_map, tensor_map(k_cache), tensor_map(v_cache), ptr(out),

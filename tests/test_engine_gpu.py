@@ -318,3 +318,32 @@ def test_bfloat16_mode_on_checkpoints_stored_in_other_types(stored, model_folder
         rows += [engine.step([slot], [ids[t:t + 1]]).cpu().numpy() for t in range(len(ids) - 5, len(ids))]
         engine.close([slot])
         assert_same_logits(np.concatenate(rows), whole, "bfloat16", f"stored {stored}, stepped")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_prefill_shape_that_repeats_is_replayed_from_a_graph(model_folders, dtype):
+    """The third step of a shape runs as a graph replay: same logits as the engine that never
+    captures, for other token ids than the graph was captured with, and after slots were
+    given back and taken again."""
+    folder = model_folders("B", dtype)
+    graphs = engine_for(folder, dtype, max_tokens=2048)
+    plain_steps = engine_for(folder, dtype, max_tokens=2048)
+    plain_steps.cuda_graphs = False
+    rng = np.random.default_rng(3)
+    lengths = [70, 5, 131]
+    for round_ in range(4):
+        prompts = [rng.integers(0, 1000, n) for n in lengths]
+        outs = []
+        for engine in (graphs, plain_steps):
+            slots = engine.open(3)
+            first = engine.step(slots, prompts)
+            second = engine.step(slots, [p[:2] for p in prompts], [[0, 1]] * 3)
+            outs.append((first.cpu().numpy(), second.cpu().numpy()))
+            engine.close(slots[::-1] if round_ % 2 else slots)
+        for got, want in zip(outs[0], outs[1]):
+            if dtype == "float32":
+                np.testing.assert_array_equal(got, want)
+            else:
+                np.testing.assert_allclose(got, want, rtol=0, atol=1e-2 * np.abs(want).max())
+    captured = [e for e in graphs._prefill_graphs.values() if isinstance(e, tuple)]
+    assert len(captured) == 2 and graphs.graph_failure is None
