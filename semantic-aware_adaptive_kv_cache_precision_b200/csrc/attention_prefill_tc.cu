@@ -3,7 +3,8 @@
 // lengths and for chunks that continue a cached prefix (the same contract as the mma.sync
 // kernel in attention_prefill.cu, which serves head size 64 and is this kernel's test twin).
 //
-//   grid  = (query tiles of up to 128 tokens, heads); block = 6 warps:
+//   grid  = (heads, work items: a query tile of up to 128 tokens and a run of its key tiles);
+//   block = 6 warps:
 //     warp 0     TMA: the query tile once, then the sequence's key/value blocks (64 keys, one
 //                cache block each) into a ring of stages,
 //     warp 1     one lane issues every tcgen05.mma and owns tensor memory,
@@ -11,10 +12,11 @@
 //                sums need no shuffles.
 //   per key tile j:   S_j = Q K_j^T      128 x 64 x 128, both operands K-major from shared
 //                                        memory, S in tensor memory (two buffers)
-//                     P_j = 2^(S_j c - m) in registers, written as bf16 to shared memory in
-//                                        the K-major swizzled layout an A operand has
-//                     O  += P_j V_j       128 x 128 x 64, V MN-major exactly as TMA wrote the
-//                                        cache block, O accumulating in tensor memory
+//                     P_j = 2^(S_j c - m) in registers, written as bf16 pairs into tensor
+//                                        memory over the first half of S_j
+//                     O  += P_j V_j       128 x 128 x 64, P the A operand from tensor memory,
+//                                        V MN-major exactly as TMA wrote the cache block, O
+//                                        accumulating in tensor memory
 //   The exponent's reference m trails the true running maximum: it is moved (and O and the
 //   row sum rescaled, in tensor memory) only when the maximum has grown by more than 2^8,
 //   so most tiles cost a row nothing but 64 exponentials. The MMA lane runs ahead: S_{j+1}
@@ -92,8 +94,8 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap q_map,
                             const int32_t* __restrict__ seq_lens,
                             const int32_t* __restrict__ block_table, int max_blocks, int heads,
                             int kv_heads, float scale_log2e, int window, int* __restrict__ error) {
-  // Exactly 112.25 KB, so that two blocks fit an SM: no slack for aligning by hand. The
-  // swizzled tiles need a 1024-byte aligned base; a block that does not get one says so.
+  // 96.25 KB, so that two blocks fit an SM. The swizzled tiles need a 1024-byte aligned
+  // base; a block that does not get one says so.
   extern __shared__ __align__(1024) uint8_t smem[];
   if (tma::smem_u32(smem) & 1023) {
     if (threadIdx.x == 0 && error) atomicCAS(error, 0, 499);
