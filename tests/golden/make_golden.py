@@ -78,4 +78,5 @@ def main(reference):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    main(sys.argv[1] if len(sys.argv) > 1
+         else str(Path(__file__).resolve().parents[3] / "reference"))

@@ -7,6 +7,7 @@ script beside them made them. If the reference checkout is present the
 comparison is also made afresh."""
 
 import hashlib
+import os
 from pathlib import Path
 
 import numpy as np
@@ -35,13 +36,19 @@ def test_plain_matches_reference_float64_model(name, model_folders):
     np.testing.assert_allclose(logits[keep], gold["logits"], rtol=0, atol=2e-6)
 
 
-@pytest.mark.skipif(not Path("/root/reference/tools/conditioning.py").is_file(),
+# the reference's checkout, if there is one beside this repository (or where
+# MICROINFER_REFERENCE points)
+REFERENCE = Path(os.environ.get("MICROINFER_REFERENCE",
+                                Path(__file__).resolve().parents[2] / "reference"))
+
+
+@pytest.mark.skipif(not (REFERENCE / "tools" / "conditioning.py").is_file(),
                     reason="no reference checkout")
 def test_plain_matches_reference_run_afresh(model_folders):
     import sys
     sys.path.insert(0, str(GOLDEN))
     from make_golden import reference_forward64
-    ModelConfig, read_tensor, forward64 = reference_forward64(Path("/root/reference"))
+    ModelConfig, read_tensor, forward64 = reference_forward64(REFERENCE)
     config, _ = TINY["A"]
     folder = model_folders("A", "float32")
     ids = prompts_for("A", [23], seed=5)[0]
