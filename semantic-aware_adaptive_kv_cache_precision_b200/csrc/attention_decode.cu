@@ -43,7 +43,16 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap k_map,
                         const int32_t* __restrict__ block_table, int max_blocks,
                         __nv_bfloat16* __restrict__ out, float* __restrict__ part_o,
                         float* __restrict__ part_ml, int heads, int kv_heads, int splits,
-                        float scale_log2e, int window, int* __restrict__ error) {
+                        float scale_log2e, int window, int* __restrict__ error,
+                        const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                        __nv_bfloat16* __restrict__ k_out, __nv_bfloat16* __restrict__ v_out) {
+  // With `cos_t`/`sin_t` (rotary tables [positions, D / 2], rotation over the whole head) the
+  // queries, keys and values in `q`'s rows are as the projection left them: this kernel
+  // rotates its queries as it loads them, and the one block of a (sequence, KV head) whose
+  // keys include the newest position rotates that key, writes it and the value into the
+  // cache (`k_out`, `v_out`: the cache entry; null when another layer owns the entry) and
+  // into its own tile. The position kernel that would do this, and the wait for it, are
+  // saved.
   using S = Smem<D>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -93,12 +102,69 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap k_map,
   };
   const int n_key_tiles = max(t1 - t0, 0);
   const int newest = n_tiles - 1 - t0;         // the tile that holds the newest key, if in this split
+  // (when this kernel itself writes the newest key, nobody before it does: every tile early)
+  const bool fused = cos_t != nullptr;
+  const bool writes = fused && k_out != nullptr && newest >= 0 && newest < n_key_tiles;
   if (threadIdx.x == 0)
     for (int i = 0; i < min(kStages, n_key_tiles); ++i)
-      if (i != newest) request(i);
+      if (i != newest || (fused && k_out != nullptr)) request(i);
+  // rotary factors of this sequence's newest position, for the columns this lane holds
+  const int pos = kv_len - 1;
+  constexpr int HS = D / 32;                     // k-steps of 16 in half a head
+  float2 cs[HS][2], sn[HS][2];
+  if (fused) {
+    const int c = (lane & 3) * 2;
+#pragma unroll
+    for (int ks = 0; ks < HS; ++ks) {
+      cs[ks][0] = *reinterpret_cast<const float2*>(cos_t + (long long)pos * (D / 2) + ks * 16 + c);
+      cs[ks][1] = *reinterpret_cast<const float2*>(cos_t + (long long)pos * (D / 2) + ks * 16 + c + 8);
+      sn[ks][0] = *reinterpret_cast<const float2*>(sin_t + (long long)pos * (D / 2) + ks * 16 + c);
+      sn[ks][1] = *reinterpret_cast<const float2*>(sin_t + (long long)pos * (D / 2) + ks * 16 + c + 8);
+    }
+  }
   wait_for_previous_kernel();
-  if (threadIdx.x == 0 && newest >= 0 && newest < min(kStages, n_key_tiles)) request(newest);
+  if (threadIdx.x == 0 && !(fused && k_out != nullptr) && newest >= 0 &&
+      newest < min(kStages, n_key_tiles))
+    request(newest);
   __syncthreads();
+
+  // The newest key and value, by the warp whose 16 keys of the tile include its row: lanes
+  // 0 .. D/16-1 take 8 sizes of the key's first half and their partners in the second, rotate
+  // them and keep both pieces; lanes 16 .. 16+D/8-1 take 8 sizes of the value.
+  const int new_row = pos % KT;
+  const bool patcher = writes && warp == new_row / 16;
+  uint4 piece_a = make_uint4(0, 0, 0, 0), piece_b = piece_a;
+  if (patcher) {
+    const __nv_bfloat16* kv = q + (long long)b * q_stride + (long long)heads * D;
+    if (lane < D / 16) {
+      const __nv_bfloat16* src = kv + (long long)g * D + lane * 8;
+      const uint4 a = *reinterpret_cast<const uint4*>(src);
+      const uint4 bb = *reinterpret_cast<const uint4*>(src + D / 2);
+      const float* ct = cos_t + (long long)pos * (D / 2) + lane * 8;
+      const float* st = sin_t + (long long)pos * (D / 2) + lane * 8;
+      const __nv_bfloat16* ap = reinterpret_cast<const __nv_bfloat16*>(&a);
+      const __nv_bfloat16* bp = reinterpret_cast<const __nv_bfloat16*>(&bb);
+      __nv_bfloat16* lo = reinterpret_cast<__nv_bfloat16*>(&piece_a);
+      __nv_bfloat16* hi = reinterpret_cast<__nv_bfloat16*>(&piece_b);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float x1 = __bfloat162float(ap[j]), x2 = __bfloat162float(bp[j]);
+        lo[j] = __float2bfloat16_rn(x1 * ct[j] - x2 * st[j]);
+        hi[j] = __float2bfloat16_rn(x2 * ct[j] + x1 * st[j]);
+      }
+    } else if (lane >= 16 && lane < 16 + D / 8) {
+      piece_a = *reinterpret_cast<const uint4*>(kv + (long long)(kv_heads + g) * D + (lane - 16) * 8);
+    }
+    // into the cache, for the steps to come
+    const int block = block_table[(long long)b * max_blocks + n_tiles - 1];
+    const long long at = (((long long)block * kv_heads + g) * KT + new_row) * D;
+    if (lane < D / 16) {
+      *reinterpret_cast<uint4*>(k_out + at + lane * 8) = piece_a;
+      *reinterpret_cast<uint4*>(k_out + at + D / 2 + lane * 8) = piece_b;
+    } else if (lane >= 16 && lane < 16 + D / 8) {
+      *reinterpret_cast<uint4*>(v_out + at + (lane - 16) * 8) = piece_a;
+    }
+  }
 
   // ---- compute warps ------------------------------------------------------------
   // Query rows of this warp's m16 tile: row r = head g*group + r, rows >= group are zero.
@@ -114,6 +180,19 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap k_map,
       qf[ks][2] = r0 < group ? *reinterpret_cast<const uint32_t*>(qb + r0 * D + col + 8) : 0u;
       qf[ks][3] = r1 < group ? *reinterpret_cast<const uint32_t*>(qb + r1 * D + col + 8) : 0u;
     }
+    if (fused) {
+#pragma unroll
+      for (int ks = 0; ks < HS; ++ks)
+#pragma unroll
+        for (int slot = 0; slot < 4; ++slot) {
+          const float2 cc = cs[ks][slot >> 1], ss = sn[ks][slot >> 1];
+          const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&qf[ks][slot]);
+          const __nv_bfloat162 bb = *reinterpret_cast<const __nv_bfloat162*>(&qf[ks + HS][slot]);
+          const float2 x1 = __bfloat1622float2(a), x2 = __bfloat1622float2(bb);
+          qf[ks][slot] = mma::pack_bf16(x1.x * cc.x - x2.x * ss.x, x1.y * cc.y - x2.y * ss.y);
+          qf[ks + HS][slot] = mma::pack_bf16(x2.x * cc.x + x1.x * ss.x, x2.y * cc.y + x1.y * ss.y);
+        }
+    }
   }
   float o[D / 8][4];
 #pragma unroll
@@ -126,6 +205,23 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap k_map,
     if (!tma::mbar_wait(&full[stage], (i / kStages) & 1, error, 102)) {
       alive = false;
       break;
+    }
+    if (patcher && i == newest) {
+      // the copy brought the row as the cache held it; this warp alone reads it
+      uint8_t* kt = smem + stage * S::kStageBytes;
+      uint8_t* vt = kt + S::kTileBytes;
+      if (lane < D / 16) {
+        const int d0 = lane * 8, d1 = D / 2 + lane * 8;
+        *reinterpret_cast<uint4*>(kt + (d0 >> 6) * (KT * 128) + new_row * 128 +
+                                  ((((d0 & 63) >> 3) ^ (new_row & 7)) << 4)) = piece_a;
+        *reinterpret_cast<uint4*>(kt + (d1 >> 6) * (KT * 128) + new_row * 128 +
+                                  ((((d1 & 63) >> 3) ^ (new_row & 7)) << 4)) = piece_b;
+      } else if (lane >= 16 && lane < 16 + D / 8) {
+        const int d0 = (lane - 16) * 8;
+        *reinterpret_cast<uint4*>(vt + (d0 >> 6) * (KT * 128) + new_row * 128 +
+                                  ((((d0 & 63) >> 3) ^ (new_row & 7)) << 4)) = piece_a;
+      }
+      __syncwarp();
     }
     const uint32_t kbase = tma::smem_u32(smem + stage * S::kStageBytes);
     const uint32_t vbase = kbase + S::kTileBytes;
@@ -324,7 +420,8 @@ template <int D>
 int launch(const CUtensorMap* k_map, const CUtensorMap* v_map, const __nv_bfloat16* q,
            long long q_stride, const int32_t* seq_lens, const int32_t* block_table, int max_blocks,
            __nv_bfloat16* out, float* part_o, float* part_ml, int sequences, int heads,
-           int kv_heads, int splits, float scale, int window, cudaStream_t stream) {
+           int kv_heads, int splits, float scale, int window, const float* cos_t,
+           const float* sin_t, __nv_bfloat16* k_out, __nv_bfloat16* v_out, cudaStream_t stream) {
   static bool configured = false;
   int* error = nullptr;
   if (cudaGetSymbolAddress(reinterpret_cast<void**>(&error), g_error) != cudaSuccess)
@@ -344,7 +441,8 @@ int launch(const CUtensorMap* k_map, const CUtensorMap* v_map, const __nv_bfloat
   int status = launch_overlapped(decode_attention_kernel<D>, grid, dim3(kThreads), Smem<D>::kBytes,
                                  stream, 1, *k_map, *v_map, q, q_stride, seq_lens, block_table,
                                  max_blocks, out, part_o, part_ml, heads, kv_heads, splits,
-                                 scale * 1.4426950408889634f, window, error);
+                                 scale * 1.4426950408889634f, window, error, cos_t,
+                                 sin_t, k_out, v_out);
   if (status == 0 && splits > 1)
     status = launch_overlapped(combine_kernel, dim3(sequences * heads), dim3(D <= 128 ? D : 128),
                                0, stream, 1, (const float*)part_o, (const float*)part_ml, out,
@@ -369,7 +467,17 @@ SAKV_EXPORT int sakv_decode_attention(const void* k_map, const void* v_map, cons
                                       const int32_t* block_table, int max_blocks, void* out,
                                       float* part_o, float* part_ml, int sequences, int heads,
                                       int kv_heads, int head_dim, int splits, float scale,
-                                      int window, cudaStream_t stream) {
+                                      int window, const float* cos_table, const float* sin_table,
+                                      void* k_cache, void* v_cache, cudaStream_t stream) {
+  // `cos_table`, `sin_table` (fp32 [positions, head_dim / 2], both or neither): `q`'s rows are
+  // then the projection's whole output [q | k | v], unrotated, and the kernel rotates the
+  // queries and, into the cache entry `k_cache`, `v_cache` (or nowhere if those are null),
+  // writes the newest position's rotated key and its value.
+  if ((cos_table == nullptr) != (sin_table == nullptr) || (k_cache == nullptr) != (v_cache == nullptr) ||
+      (k_cache && !cos_table) || ((uintptr_t)cos_table & 7) || ((uintptr_t)sin_table & 7) ||
+      ((uintptr_t)k_cache & 15) || ((uintptr_t)v_cache & 15) ||
+      (cos_table && (((uintptr_t)q & 15) || (q_stride & 7))))
+    return cudaErrorInvalidValue;
   if (sequences < 0 || heads <= 0 || kv_heads <= 0 || heads % kv_heads || heads / kv_heads > 16 ||
       splits < 1 || max_blocks <= 0 || (splits > 1 && (!part_o || !part_ml || (reinterpret_cast<uintptr_t>(part_ml) & 7))))
     return cudaErrorInvalidValue;
@@ -379,7 +487,8 @@ SAKV_EXPORT int sakv_decode_attention(const void* k_map, const void* v_map, cons
   return launch<D>((const CUtensorMap*)k_map, (const CUtensorMap*)v_map,                      \
                    (const __nv_bfloat16*)q, q_stride, seq_lens, block_table, max_blocks,      \
                    (__nv_bfloat16*)out, part_o, part_ml, sequences, heads, kv_heads, splits,  \
-                   scale, window, stream)
+                   scale, window, cos_table, sin_table, (__nv_bfloat16*)k_cache,              \
+                   (__nv_bfloat16*)v_cache, stream)
   if (head_dim == 64) GO(64);
   if (head_dim == 128) GO(128);
 #undef GO
@@ -455,9 +564,9 @@ SAKV_EXPORT int sakv_decode_attention_static_scratch(
     return launch<64>((const CUtensorMap*)k_map, (const CUtensorMap*)v_map,
                       (const __nv_bfloat16*)q, q_stride, seq_lens, block_table, max_blocks,
                       (__nv_bfloat16*)out, part_o, part_ml, sequences, heads, kv_heads, splits,
-                      scale, window, stream);
+                      scale, window, nullptr, nullptr, nullptr, nullptr, stream);
   return launch<128>((const CUtensorMap*)k_map, (const CUtensorMap*)v_map,
                      (const __nv_bfloat16*)q, q_stride, seq_lens, block_table, max_blocks,
                      (__nv_bfloat16*)out, part_o, part_ml, sequences, heads, kv_heads, splits,
-                     scale, window, stream);
+                     scale, window, nullptr, nullptr, nullptr, nullptr, stream);
 }

@@ -58,8 +58,13 @@ def decode_splits(sequences: int, kv_heads: int, max_len: int) -> int:
 def attention_decode(qkv: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                      seq_lens: torch.Tensor, block_table: torch.Tensor, heads: int, kv_heads: int,
                      head_dim: int, scale: float, window, max_len: int,
-                     splits: int | None = None) -> torch.Tensor:
-    """One query token per sequence (row b of `qkv` belongs to sequence b)."""
+                     splits: int | None = None, rotary=None, write_cache: bool = True) -> torch.Tensor:
+    """One query token per sequence (row b of `qkv` belongs to sequence b).
+
+    `rotary`: None, or `(cos, sin)` (fp32 [positions, head_dim / 2], rotation over the whole
+    head): `qkv` is then the projection's output as it came, [q | k | v] unrotated, and the
+    kernel rotates the queries on its way and (`write_cache`) puts the newest position's
+    rotated key and its value into the cache; `ops.rope_store` is not called for the step."""
     require_cuda(qkv, k_cache, v_cache, seq_lens, block_table)
     sequences = qkv.shape[0]
     if not fast_path_takes(qkv.dtype, heads, kv_heads, head_dim):
@@ -80,8 +85,27 @@ def attention_decode(qkv: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Te
     call("sakv_decode_attention", tensor_map(k_cache), tensor_map(v_cache), ptr(qkv),
          qkv.stride(0), ptr(seq_lens), ptr(block_table), block_table.shape[1], ptr(out),
          ptr(part_o), ptr(part_ml), sequences, heads, kv_heads, head_dim, splits, float(scale),
-         int(window) if window else 0)
+         int(window) if window else 0, *_rotary_arguments(rotary, write_cache, qkv, k_cache, v_cache,
+                                                         heads, kv_heads, head_dim, max_len))
     return out
+
+
+def _rotary_arguments(rotary, write_cache, qkv, k_cache, v_cache, heads, kv_heads, head_dim,
+                      max_len):
+    if rotary is None:
+        return None, None, None, None
+    cos, sin = rotary
+    if cos.dtype != torch.float32 or sin.dtype != torch.float32 or cos.shape != sin.shape \
+            or cos.dim() != 2 or cos.shape[1] * 2 != head_dim or not cos.is_contiguous() \
+            or not sin.is_contiguous():
+        raise KernelError("attention_decode: rotary tables must be fp32 [positions, head_dim / 2]")
+    if qkv.shape[1] != (heads + 2 * kv_heads) * head_dim or qkv.data_ptr() % 16 \
+            or qkv.stride(0) % 8:
+        raise KernelError("attention_decode: with rotary tables qkv must be the whole "
+                          "[q | k | v] projection, rows 16-byte aligned")
+    if write_cache:
+        return ptr(cos), ptr(sin), ptr(k_cache), ptr(v_cache)
+    return ptr(cos), ptr(sin), None, None
 
 
 def attention_prefill(qkv: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,

@@ -81,12 +81,19 @@ class GQAAttention(Part):
     def forward(self, h, step, view, residual, write_cache=True, defer=False):
         s = self.spec
         qkv = ops.linear(h, self.w_qkv, self.b_qkv, out_dtype=self.act_dtype)
-        self.position.rotate_store(qkv, step, view, s.heads, s.kv_heads, s.head_dim, write_cache)
-        attended = self.attend(qkv, step, view)
+        rotary = None
+        if step.is_decode and ops.fast_path_takes(qkv.dtype, s.heads, s.kv_heads, s.head_dim) \
+                and hasattr(self.position, "tables"):
+            # one token a sequence: the attention kernel rotates and stores on its own way
+            rotary = self.position.tables(step, s.head_dim)
+        if rotary is None:
+            self.position.rotate_store(qkv, step, view, s.heads, s.kv_heads, s.head_dim,
+                                       write_cache)
+        attended = self.attend(qkv, step, view, rotary, write_cache)
         out = ops.linear(attended, self.w_o, self.b_o, accumulate_into=residual, may_defer=defer)
         return out.delta if isinstance(out, ops.Deferred) else None
 
-    def attend(self, qkv, step, view):
+    def attend(self, qkv, step, view, rotary=None, write_cache=True):
         """Tensor-core kernels where they take the sizes (bf16, head_dim 64 or 128, up
         to 16 query heads per KV head): the split-key decode kernel when every
         sequence brings one token; otherwise the causal prefill kernels, tcgen05 for
@@ -97,7 +104,8 @@ class GQAAttention(Part):
             if step.is_decode:
                 return ops.attention_decode(qkv, view.keys, view.values, step.seq_lens,
                                             view.block_table, s.heads, s.kv_heads, s.head_dim,
-                                            s.scale, s.window, step.max_len_bound or step.max_len)
+                                            s.scale, s.window, step.max_len_bound or step.max_len,
+                                            rotary=rotary, write_cache=write_cache)
             if ops.tc_prefill_takes(qkv.dtype, s.heads, s.kv_heads, s.head_dim) and step.starts:
                 key = ("wide_tiles", s.heads, s.window)
                 plan = step.plans.get(key)

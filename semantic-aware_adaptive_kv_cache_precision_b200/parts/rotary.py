@@ -35,6 +35,14 @@ class RotaryHalf(Part):
         self.cos = torch.from_numpy(np.cos(angle).astype(np.float32)).to(device)
         self.sin = torch.from_numpy(np.sin(angle).astype(np.float32)).to(device)
 
+    def tables(self, step, head_dim):
+        """(cos, sin) for a kernel that rotates on its own way (the decode attention), or None
+        if this encoding is not a rotation over the whole head of positions the tables hold."""
+        if self.spec.rotary_dim != head_dim or self.cos.dtype != torch.float32 \
+                or step.max_position >= self.cos.shape[0]:
+            return None
+        return self.cos, self.sin
+
     def rotate_store(self, qkv, step, view, heads, kv_heads, head_dim, write_cache=True):
         if step.max_position >= self.cos.shape[0]:
             raise ValueError(f"position {step.max_position} is beyond the rotary table of "

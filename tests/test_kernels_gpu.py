@@ -407,6 +407,54 @@ def test_attention_decode_kernel(heads, kv_heads, d, window, splits):
     np.testing.assert_allclose(host(got), host(plain_out), rtol=0, atol=2e-2)
 
 
+@pytest.mark.parametrize("heads,kv_heads,d,window,splits", [
+    (12, 2, 128, None, None), (12, 2, 128, None, 1), (2, 1, 64, None, 3), (6, 6, 64, 70, None),
+    (7, 1, 128, 200, 5), (16, 1, 128, None, 2)])
+def test_attention_decode_rotates_and_stores_on_its_way(heads, kv_heads, d, window, splits):
+    """With rotary tables the decode kernel takes the projection's output as it came: what it
+    returns, and what it leaves in the cache, is what the position kernel followed by the
+    decode kernel gives; with `write_cache=False` the cache is only read."""
+    rng = np.random.default_rng(heads * d + (window or 0))
+    lengths = [1, 63, 64, 65, 700, 2048, 129, 128]
+    k_cache, v_cache, table = paged_case(rng, lengths, kv_heads, d)
+    if window:
+        for i, n in enumerate(lengths):
+            table[i, :max(0, n - window) // 64] = -1
+    B = len(lengths)
+    width = (heads + 2 * kv_heads) * d
+    qkv = dev(rng.standard_normal((B, width)), torch.bfloat16)
+    j = np.arange(d // 2)
+    angle = np.arange(2304)[:, None] * np.power(1e4, -2.0 * j / d)[None, :]
+    cos, sin = dev(np.cos(angle)), dev(np.sin(angle))
+    lens, tab = dev(lengths, torch.int32), dev(table, torch.int32)
+    scale = d ** -0.5
+    # the two kernels, one after the other
+    k_two, v_two, q_two = k_cache.clone(), v_cache.clone(), qkv.clone()
+    ops.rope_store(q_two, dev([n - 1 for n in lengths], torch.int32), dev(np.arange(B), torch.int32),
+                   tab, cos, sin, k_two, v_two, heads, kv_heads, d)
+    want = ops.attention_decode(q_two, k_two, v_two, lens, tab, heads, kv_heads, d, scale, window,
+                                max(lengths), splits=splits)
+    # the one kernel
+    k_one, v_one = k_cache.clone(), v_cache.clone()
+    got = ops.attention_decode(qkv, k_one, v_one, lens, tab, heads, kv_heads, d, scale, window,
+                               max(lengths), splits=splits, rotary=(cos, sin))
+    assert all(v == 0 for v in ops.kernel_errors().values())
+    np.testing.assert_allclose(host(got), host(want), rtol=0, atol=4e-3)
+    np.testing.assert_allclose(host(k_one), host(k_two), rtol=0, atol=2.0 ** -6)
+    np.testing.assert_array_equal(host(v_one), host(v_two))       # (NaN in unused blocks)
+    for now, was in ((k_one, k_cache), (v_one, v_cache)):
+        a, b = host(now), host(was)
+        changed = ((a != b) & ~(np.isnan(a) & np.isnan(b))).any(axis=(1, 3))     # [block, row]
+        assert changed.sum() <= B
+    # a layer that reads another layer's cache: the newest key is there already
+    k_read, v_read = k_two.clone(), v_two.clone()
+    again = ops.attention_decode(qkv, k_read, v_read, lens, tab, heads, kv_heads, d, scale, window,
+                                 max(lengths), splits=splits, rotary=(cos, sin), write_cache=False)
+    np.testing.assert_allclose(host(again), host(want), rtol=0, atol=4e-3)
+    np.testing.assert_array_equal(host(k_read), host(k_two))
+    np.testing.assert_array_equal(host(v_read), host(v_two))
+
+
 @pytest.mark.parametrize("heads,kv_heads,d,window", [(12, 2, 128, None), (2, 1, 64, None),
                                                      (6, 6, 64, 70), (7, 1, 128, 200)])
 def test_attention_prefill_kernel(heads, kv_heads, d, window):
