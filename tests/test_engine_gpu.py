@@ -347,3 +347,25 @@ def test_a_prefill_shape_that_repeats_is_replayed_from_a_graph(model_folders, dt
                 np.testing.assert_allclose(got, want, rtol=0, atol=1e-2 * np.abs(want).max())
     captured = [e for e in graphs._prefill_graphs.values() if isinstance(e, tuple)]
     assert len(captured) == 2 and graphs.graph_failure is None
+
+
+def test_many_requests_in_batches_end_as_they_do_alone(model_folders):
+    """Twenty-three requests of unequal lengths through batches of five, with a stop token
+    that ends some of them early: each gets the tokens it gets alone (fp32: the same to the
+    token), every slot comes back, and the endings say why."""
+    folder = model_folders("A", "float32")
+    engine = engine_for(folder, "float32", max_tokens=1024, max_batch=5)
+    alone = engine_for(folder, "float32", max_tokens=1024, max_batch=1)
+    rng = np.random.default_rng(11)
+    prompts = [rng.integers(0, 512, int(n)).tolist() for n in rng.integers(1, 40, 23)]
+    free = [alone.generate(p, 12, stop_at_eos=False).tolist() for p in prompts]
+    counts = np.bincount(np.concatenate(free), minlength=512)
+    stop = int(counts.argmax())                    # a token many of them produce
+    want = [w[:w.index(stop) + 1] if stop in w else w for w in free]
+    assert any(len(w) < 12 for w in want) and any(len(w) == 12 for w in want)
+    got = engine.generate(prompts, 12, stop_token_ids=[stop])
+    assert [g.tolist() for g in got] == want
+    assert [e.reason for e in engine.endings] == ["stop" if w[-1] == stop else "length" for w in want]
+    assert [e.positions for e in engine.endings] == [len(p) + len(w) - 1 for p, w in zip(prompts, want)]
+    assert engine.cache.slots.held == 0
+    engine.cache.check()
