@@ -44,6 +44,7 @@ LIBRARIES = {
     "attention_prefill": "attention_prefill.cu",
     "attention_prefill_tc": "attention_prefill_tc.cu",
     "gemm_tc": "gemm_tc.cu",
+    "gemm_wide": "gemm_wide.cu",
 }
 
 #: extra flags of single libraries (libraries that need the driver API, for instance)

@@ -37,6 +37,7 @@ SIGNATURES = {
     "sakv_prefill_attention_tc": ("attention_prefill_tc",
                                   [P, P, P, P, P, I, P, I, P, P, P, P, I, I, I, I, F, I, P]),
     "sakv_gemm_tc": ("gemm_tc", [P, P, I, I, I, I, I, I, I, I, P, I, P, L, L, P]),
+    "sakv_gemm_wide": ("gemm_wide", [P, P, I, I, I, I, P, L, P]),
 }
 
 #: functions without a stream argument: (library, argument types)
@@ -48,6 +49,8 @@ PLAIN_SIGNATURES = {
     "sakv_prefill_attention_tc_error": ("attention_prefill_tc", [P]),
     "sakv_prefill_attention_tc_qmap": ("attention_prefill_tc", [P, P, L, L, L]),
     "sakv_gemm_tc_map": ("gemm_tc", [P, P, L, L, L, I]),
+    "sakv_gemm_wide_map": ("gemm_wide", [P, P, L, L, L]),
+    "sakv_gemm_wide_error": ("gemm_wide", [P]),
     "sakv_gemm_tc_splits": ("gemm_tc", [I, I]),
     "sakv_gemm_tc_max_clusters": ("gemm_tc", [I, I, I]),
     "sakv_gemm_tc_error": ("gemm_tc", [P]),

@@ -584,6 +584,28 @@ def test_gemm_tc_k_ranges_summed_apart(M, N, K, parts, splits):
     assert torch.equal(stream, apart) and torch.equal(got_normed, want_normed)
 
 
+@pytest.mark.parametrize("M,I,K", [(1030, 384, 1536), (256, 200, 72), (2048, 8960, 1536),
+                                   (700, 128, 64), (513, 1096, 328)])
+def test_gated_product_for_many_tokens(M, I, K):
+    """The tcgen05 product with the gated SiLU in its epilogue against float64, and against
+    the library's product followed by the activation kernel (a bf16 rounding apart)."""
+    from semantic_aware_adaptive_kv_cache_precision_b200.ops import gemm_wide
+    rng = np.random.default_rng(M + I + K)
+    x = dev(rng.standard_normal((M, K)), torch.bfloat16)
+    w = dev(rng.standard_normal((2 * I, K)) * (2.0 / np.sqrt(K)), torch.bfloat16)
+    assert gemm_wide.takes(x, w)
+    got = host(gemm_wide.gated(x, w))
+    assert gemm_wide.error_word() == 0
+    both = host(x) @ host(w).T
+    gate, up = both[:, :I], both[:, I:]
+    want = gate / (1 + np.exp(-gate)) * up
+    assert np.abs(got - want).max() <= 2.0 ** -8 * (np.abs(want).max() + 1) * 1.5
+    twin = host(ops.gated_silu(torch.mm(x, w.t())))
+    assert np.abs(got - twin).max() <= 2.0 ** -7 * (np.abs(want).max() + 1)
+    if M >= gemm_wide.MIN_TOKENS:
+        assert torch.equal(ops.gated_up(x, w), gemm_wide.gated(x, w))    # the product path takes it
+
+
 def test_linear_hands_back_k_ranges_only_when_asked():
     rng = np.random.default_rng(5)
     x = dev(rng.standard_normal((8, 8960)), torch.bfloat16)
