@@ -21,7 +21,8 @@
 //   warp 0     TMA: per K step of 64 two boxes of x [128 x 64] and two boxes of W [128 x 64]
 //              into a ring of three 64 KB stages (128-byte swizzle),
 //   warp 1     one lane issues every tcgen05.mma and commits stages and accumulators,
-//   warps 2-5  epilogue: thread = token row (tensor-memory lane); reads its gate and up sums
+//   warps 2-9  epilogue, four warps for each of the tile's two products (a warp reaches the
+//              32 lanes of its number modulo 4): thread = token row; reads its gate and up sums
 //              16 at a time, applies silu(g) * u in fp32, stores 32 bytes at a time.
 //
 // The reference calls cuBLAS for every projection and runs SwiGLU as a kernel of its own
@@ -42,7 +43,7 @@ constexpr int kStages = 3;
 constexpr int kXBytes = kHalves * BM * BK * 2;  // 32 KB: two boxes of 128 tokens
 constexpr int kWBytes = BN * BK * 2;            // 32 KB: two boxes of 128 rows
 constexpr int kStageBytes = kXBytes + kWBytes;  // 64 KB
-constexpr int kThreads = 192;
+constexpr int kThreads = 64 + kHalves * 128;     // TMA, MMA, and four epilogue warps a product
 constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
 constexpr uint32_t kTmemCols = 512;
 
@@ -167,7 +168,8 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constan
       const int m_tile = tile % p.m_tiles, n_tile = tile / p.m_tiles;
       ok = ok && tma::mbar_wait(&bar->acc_full, round & 1, p.error, 604);
       tc::fence_after_sync();
-      for (int h = 0; h < kHalves; ++h) {
+      {
+        const int h = (warp - 2) >> 2;            // which of the tile's two products
         const int m = (m_tile * kHalves + h) * BM + row;
         const uint32_t acc = lane_base + h * BN;
         const int n0 = n_tile * 128;
