@@ -273,7 +273,11 @@ def kernel_case(name: str) -> int:
     def weights(n, k, copies):
         return [torch.randn(n, k, device=dev, dtype=torch.bfloat16) * 0.02 for _ in range(copies)]
 
-    if name.startswith("gemm_"):
+    if name == "gemm_gated_2048":
+        from semantic_aware_adaptive_kv_cache_precision_b200.ops import gemm_wide
+        ws, x = weights(2 * I, H, 3), torch.randn(PREFILL_TOKENS, H, device=dev, dtype=torch.bfloat16)
+        run = lambda i: gemm_wide.gated(x, ws[i % 3])
+    elif name.startswith("gemm_"):
         _, which, batch = name.split("_", 2)
         m = int(batch.lstrip("b"))
         if which == "gateup":
@@ -325,7 +329,8 @@ def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--kernel", default=None,
                     help="run one kernel case for a profiler: gemm_gateup_b8, gemm_down_b8, "
-                         "gemm_head_b8, attention_decode_b64, attention_prefill_2048")
+                         "gemm_head_b8, gemm_gated_2048, attention_decode_b64, "
+                         "attention_prefill_2048")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=3)
