@@ -21,6 +21,26 @@ namespace {
 constexpr int kThreads = 256;
 constexpr int kPerThread = 4;          // float4 loads per thread: rows up to 4096 wide
 
+// Four weights, or four results, in one access where the type allows it.
+__device__ __forceinline__ void load4(const float* p, float (&w)[4]) {
+  const float4 v = *reinterpret_cast<const float4*>(p);
+  w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w;
+}
+__device__ __forceinline__ void load4(const __nv_bfloat16* p, float (&w)[4]) {
+  const uint2 raw = *reinterpret_cast<const uint2*>(p);
+  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+  const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+  w[0] = a.x; w[1] = a.y; w[2] = b.x; w[3] = b.y;
+}
+__device__ __forceinline__ void store4(float* p, float a, float b, float c, float d) {
+  *reinterpret_cast<float4*>(p) = make_float4(a, b, c, d);
+}
+__device__ __forceinline__ void store4(__nv_bfloat16* p, float a, float b, float c, float d) {
+  const __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+  *reinterpret_cast<uint2*>(p) = make_uint2(*reinterpret_cast<const uint32_t*>(&lo),
+                                            *reinterpret_cast<const uint32_t*>(&hi));
+}
+
 template <typename W, typename Out, bool kAdd = false>
 __global__ void __launch_bounds__(kThreads)
 rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ add,
@@ -28,16 +48,14 @@ rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ add,
                const W* __restrict__ weight, Out* __restrict__ out, int hidden, float eps) {
   __shared__ float scratch[33];
   let_next_kernel_start();
-  const bool fits = hidden <= kThreads * 4 * kPerThread && (hidden & 3) == 0;
+  const bool fits = hidden <= kThreads * 4 * kPerThread && (hidden & 3) == 0 &&
+                    !((reinterpret_cast<uintptr_t>(weight) | reinterpret_cast<uintptr_t>(out)) & 15);
   float wv[kPerThread][4];
   if (fits) {                      // the weight does not depend on the kernel before
 #pragma unroll
     for (int i = 0; i < kPerThread; ++i) {
       const int c = (i * kThreads + threadIdx.x) * 4;
-      if (c < hidden) {
-#pragma unroll
-        for (int j = 0; j < 4; ++j) wv[i][j] = widen(weight[c + j]);
-      }
+      if (c < hidden) load4(weight + c, wv[i]);
     }
   }
   wait_for_previous_kernel();
@@ -74,12 +92,9 @@ rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ add,
 #pragma unroll
     for (int i = 0; i < kPerThread; ++i) {
       const int c = (i * kThreads + threadIdx.x) * 4;
-      if (c < hidden) {
-        o[c] = narrow<Out>(v[i].x * scale * wv[i][0]);
-        o[c + 1] = narrow<Out>(v[i].y * scale * wv[i][1]);
-        o[c + 2] = narrow<Out>(v[i].z * scale * wv[i][2]);
-        o[c + 3] = narrow<Out>(v[i].w * scale * wv[i][3]);
-      }
+      if (c < hidden)
+        store4(o + c, v[i].x * scale * wv[i][0], v[i].y * scale * wv[i][1],
+               v[i].z * scale * wv[i][2], v[i].w * scale * wv[i][3]);
     }
     return;
   }
