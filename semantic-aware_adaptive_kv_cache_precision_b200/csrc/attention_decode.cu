@@ -89,9 +89,15 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap k_map,
 
   // Tile i of this split goes to stage i % kStages. Lane 0 of warp 0 keeps the ring full:
   // kStages tiles to begin with, then tile i + kStages once every warp has let go of tile i.
-  auto request = [&](int i) {
+  // (The cache blocks of the split's first kListed tiles are fetched once, by a thread each,
+  // before the wait: a request between two tiles then finds its block in shared memory
+  // instead of paying a trip to global memory in the middle of the loop.)
+  constexpr int kListed = kThreads;
+  __shared__ int listed[kListed];
+  auto request = [&](int i, bool from_list) {
     const int stage = i % kStages;
-    const int block = block_table[(long long)b * max_blocks + t0 + i];
+    const int block = from_list && i < kListed ? listed[i]
+                                               : block_table[(long long)b * max_blocks + t0 + i];
     const int row0 = (block * kv_heads + g) * KT;
     uint8_t* dst = smem + stage * S::kStageBytes;
     tma::mbar_expect_tx(&full[stage], S::kStageBytes);
@@ -107,7 +113,9 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap k_map,
   const bool writes = fused && k_out != nullptr && newest >= 0 && newest < n_key_tiles;
   if (threadIdx.x == 0)
     for (int i = 0; i < min(kStages, n_key_tiles); ++i)
-      if (i != newest || (fused && k_out != nullptr)) request(i);
+      if (i != newest || (fused && k_out != nullptr)) request(i, false);
+  if (threadIdx.x < n_key_tiles)
+    listed[threadIdx.x] = block_table[(long long)b * max_blocks + t0 + threadIdx.x];
   // rotary factors of this sequence's newest position, for the columns this lane holds
   const int pos = kv_len - 1;
   constexpr int HS = D / 32;                     // k-steps of 16 in half a head
@@ -125,7 +133,7 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap k_map,
   wait_for_previous_kernel();
   if (threadIdx.x == 0 && !(fused && k_out != nullptr) && newest >= 0 &&
       newest < min(kStages, n_key_tiles))
-    request(newest);
+    request(newest, false);
   __syncthreads();
 
   // The newest key and value, by the warp whose 16 keys of the tile include its row: lanes
@@ -310,7 +318,7 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap k_map,
       tma::mbar_arrive(&empty[stage]);
       if (warp == 0 && i + kStages < n_key_tiles) {
         if (!tma::mbar_wait(&empty[stage], (i / kStages) & 1, error, 101)) alive = false;
-        else request(i + kStages);
+        else request(i + kStages, true);
       }
     }
     alive = __shfl_sync(0xffffffffu, alive, 0);
@@ -334,8 +342,8 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap k_map,
     for (int nt = 0; nt < D / 8; ++nt) {
       float* row0 = sm_o + (warp * 16 + r0) * kRow + nt * 8 + c;
       float* row1 = row0 + 8 * kRow;
-      row0[0] = o[nt][0]; row0[1] = o[nt][1];
-      row1[0] = o[nt][2]; row1[1] = o[nt][3];
+      *reinterpret_cast<float2*>(row0) = make_float2(o[nt][0], o[nt][1]);
+      *reinterpret_cast<float2*>(row1) = make_float2(o[nt][2], o[nt][3]);
     }
     if ((lane & 3) == 0) {
       sm_m[warp * 16 + r0] = m[0]; sm_m[warp * 16 + r0 + 8] = m[1];
@@ -344,7 +352,10 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap k_map,
   }
   asm volatile("bar.sync 1, %0;" ::"n"(kComputeWarps * 32));
   if (!alive) return;
-  for (int r = 0; r < group; ++r) {
+  // a warp takes query heads warp, warp + 4, ...; a lane four sizes of the head: one 16-byte
+  // read per warp's share of a row, one 16-byte (bf16: 8-byte) store
+#pragma unroll 2
+  for (int r = warp; r < group; r += kComputeWarps) {
     float big = -INFINITY;
 #pragma unroll
     for (int w = 0; w < kComputeWarps; ++w) big = fmaxf(big, sm_m[w * 16 + r]);
@@ -355,17 +366,24 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap k_map,
       total += weight[w] * sm_l[w * 16 + r];
     }
     const int h = g * group + r;
-    for (int dim = threadIdx.x; dim < D; dim += kComputeWarps * 32) {
-      float acc = 0.f;
+    if (lane < D / 4) {
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-      for (int w = 0; w < kComputeWarps; ++w) acc += weight[w] * sm_o[(w * 16 + r) * kRow + dim];
+      for (int w = 0; w < kComputeWarps; ++w) {
+        const float4 v = *reinterpret_cast<const float4*>(sm_o + (w * 16 + r) * kRow + lane * 4);
+        acc.x += weight[w] * v.x; acc.y += weight[w] * v.y;
+        acc.z += weight[w] * v.z; acc.w += weight[w] * v.w;
+      }
       if (splits == 1) {
-        out[((long long)b * heads + h) * D + dim] = __float2bfloat16_rn(acc / total);
+        *reinterpret_cast<uint2*>(out + ((long long)b * heads + h) * D + lane * 4) =
+            make_uint2(mma::pack_bf16(acc.x / total, acc.y / total),
+                       mma::pack_bf16(acc.z / total, acc.w / total));
       } else {
-        part_o[(((long long)b * heads + h) * splits + split) * D + dim] = acc;
+        *reinterpret_cast<float4*>(part_o + (((long long)b * heads + h) * splits + split) * D +
+                                   lane * 4) = acc;
       }
     }
-    if (splits > 1 && threadIdx.x == 0) {
+    if (splits > 1 && lane == 0) {
       float* ml = part_ml + (((long long)b * heads + h) * splits + split) * 2;
       ml[0] = big;
       ml[1] = total;
