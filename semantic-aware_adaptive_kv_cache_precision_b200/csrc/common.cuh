@@ -81,7 +81,7 @@ static inline int launch_overlapped(void (*kernel)(KernelArgs...), dim3 grid, di
   config.blockDim = block;
   config.dynamicSmemBytes = smem;
   config.stream = stream;
-  cudaLaunchAttribute attr[2];
+  cudaLaunchAttribute attr[3];
   int n = 0;
   attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[n].val.programmaticStreamSerializationAllowed = 1;
@@ -91,6 +91,10 @@ static inline int launch_overlapped(void (*kernel)(KernelArgs...), dim3 grid, di
     attr[n].val.clusterDim.x = 1;
     attr[n].val.clusterDim.y = 1;
     attr[n].val.clusterDim.z = cluster_z;
+    ++n;
+    // (the blocks of a cluster are there to pull weights through as many SMs as possible)
+    attr[n].id = cudaLaunchAttributeClusterSchedulingPolicyPreference;
+    attr[n].val.clusterSchedulingPolicyPreference = cudaClusterSchedulingPolicySpread;
     ++n;
   }
   config.attrs = attr;
