@@ -28,6 +28,8 @@ from __future__ import annotations
 import argparse
 import json
 import os
+import select
+import datetime
 import statistics
 import subprocess
 import sys
@@ -76,48 +78,68 @@ def peaks() -> dict:
 
 
 class ClockSampler:
-    """nvidia-smi in the background, sampling SM clocks and throttle reasons."""
+    """nvidia-smi in the background, sampling SM clocks and throttle reasons every 20 ms; the
+    samples whose time stamps fall between `begin()` and `end()` (the timed region) are the
+    ones reported, all of them if the region was too short to catch any."""
 
-    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+    QUERY = ("timestamp,clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
              "clocks_event_reasons.sw_power_cap")
 
     def __init__(self):
         self.proc = None
+        self.began = self.ended = None
 
     def start(self):
+        """Start sampling (well before the timed region: the tool takes a moment to come up)."""
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", "20"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            # its first line says that it is up (at most 3 s are spent waiting for it)
+            if select.select([self.proc.stdout], [], [], 3.0)[0]:
+                self.proc.stdout.readline()
         except OSError:
             self.proc = None
+
+    def begin(self):
+        self.began = datetime.datetime.now()
+
+    def end(self):
+        self.ended = datetime.datetime.now()
 
     def stop(self) -> dict:
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        if self.ended is None:
+            self.ended = datetime.datetime.now()
         self.proc.terminate()
         try:
             out, _ = self.proc.communicate(timeout=5)
         except subprocess.TimeoutExpired:
             self.proc.kill()
             out, _ = self.proc.communicate()
-        clocks, top, reasons = [], None, set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        samples, top = [], None
         for line in out.splitlines():
             parts = [p.strip() for p in line.split(",")]
-            if len(parts) != 6:
+            if len(parts) != 7:
                 continue
             try:
-                clocks.append(float(parts[0]))
-                top = float(parts[1])
+                when = datetime.datetime.strptime(parts[0], "%Y/%m/%d %H:%M:%S.%f")
+                clock = float(parts[1])
+                top = float(parts[2])
             except ValueError:
                 continue
-            for name, flag in zip(names, parts[2:]):
-                if flag.lower().startswith("active"):
-                    reasons.add(name)
-        return {"sm_mhz": statistics.median(clocks) if clocks else None, "sm_max_mhz": top,
-                "reasons": sorted(reasons), "samples": len(clocks)}
+            active = {name for name, flag in zip(names, parts[3:]) if flag.lower().startswith("active")}
+            samples.append((when, clock, active))
+        inside = [x for x in samples if self.began is not None and self.began <= x[0] <= self.ended]
+        window = "timed region" if inside else "whole run"
+        used = inside or samples
+        reasons = set().union(*(x[2] for x in used)) if used else set()
+        return {"sm_mhz": statistics.median(x[1] for x in used) if used else None,
+                "sm_max_mhz": top, "reasons": sorted(reasons), "samples": len(used),
+                "window": window}
 
 
 def decode_bytes(cfg, batch: int, context: int) -> int:
@@ -220,11 +242,13 @@ def reference_arm(args) -> int:
                 timed(prompts[0], 4)
             sampler = ClockSampler()
             sampler.start()
+            sampler.begin()
             decode_s, prefill_s = 0.0, []
             for ids in prompts:
                 first = timed(ids, 1)
                 decode_s += max(timed(ids, K + 1) - first, 1e-9)
                 prefill_s.append(first)
+            sampler.end()
             clocks = sampler.stop()
         finally:
             shutil.rmtree(tmp, ignore_errors=True)
@@ -407,17 +431,19 @@ def main() -> int:
             read.append(host)
             return chosen
 
+        sampler = ClockSampler()
+        sampler.start()
         for _ in range(warmup):
             chosen = one(chosen)
         torch.cuda.synchronize()
         launches0 = _lib.launches
-        sampler = ClockSampler()
-        sampler.start()
+        sampler.begin()
         start.record()
         for _ in range(steps):
             chosen = one(chosen)
         stop.record()
         torch.cuda.synchronize()
+        sampler.end()
         clocks = sampler.stop()
         ms = start.elapsed_time(stop)
         assert all(0 <= int(t) < cfg.vocab_size for host in read for t in host.tolist())
