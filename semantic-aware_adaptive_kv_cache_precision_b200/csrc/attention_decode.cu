@@ -432,6 +432,65 @@ __global__ void combine_kernel(const float* __restrict__ part_o, const float* __
   }
 }
 
+// The same for more than 16 splits (one sequence, or few): the block has several groups of
+// `head_dim` threads (`blockDim.x = groups * head_dim`, at most kFoldGroups); group j takes
+// rounds j, j + groups, ..., so that up to 64 splits still cost one round trip, and group 0
+// merges the groups' results through shared memory, always in the order of the groups.
+// (Kept apart from the kernel above: with both in one, the decode step at 8 sequences, which
+// has one group, was 1.5 % slower.)
+constexpr int kFoldGroups = 4;
+__global__ void combine_groups_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                               __nv_bfloat16* __restrict__ out, int splits, int head_dim) {
+  let_next_kernel_start();
+  wait_for_previous_kernel();
+  constexpr int kRound = 16;
+  extern __shared__ float3 merged[];      // [groups - 1][head_dim]; nothing for one group
+  const long long bh = blockIdx.x;
+  const float2* ml = reinterpret_cast<const float2*>(part_ml) + bh * splits;
+  const int groups = blockDim.x / head_dim, group = threadIdx.x / head_dim;
+  const int dim = threadIdx.x - group * head_dim;
+  float big = -INFINITY, total = 0.f, acc = 0.f;
+  for (int s0 = group * kRound; s0 < splits; s0 += groups * kRound) {
+    float2 v[kRound];
+    float o[kRound];
+#pragma unroll
+    for (int j = 0; j < kRound; ++j) {
+      const bool live = s0 + j < splits;
+      v[j] = live ? ml[s0 + j] : make_float2(-INFINITY, 0.f);
+      o[j] = live ? part_o[(bh * splits + s0 + j) * head_dim + dim] : 0.f;
+    }
+    float round_max = big;
+#pragma unroll
+    for (int j = 0; j < kRound; ++j) round_max = fmaxf(round_max, v[j].x);
+    if (round_max == -INFINITY) continue;
+    const float keep = exp2f(big - round_max);          // 0 the first time
+    total *= keep;
+    acc *= keep;
+    big = round_max;
+#pragma unroll
+    for (int j = 0; j < kRound; ++j) {
+      const float w = exp2f(v[j].x - big);              // 0 for a split that saw no key
+      total += w * v[j].y;
+      acc += w * o[j];
+    }
+  }
+  if (groups > 1) {
+    if (group > 0) merged[(group - 1) * head_dim + dim] = make_float3(big, total, acc);
+    __syncthreads();
+    if (group > 0) return;
+    for (int j = 0; j < groups - 1; ++j) {
+      const float3 other = merged[j * head_dim + dim];
+      const float top = fmaxf(big, other.x);
+      if (top == -INFINITY) continue;
+      const float mine = exp2f(big - top), theirs = exp2f(other.x - top);
+      total = total * mine + other.y * theirs;
+      acc = acc * mine + other.z * theirs;
+      big = top;
+    }
+  }
+  out[bh * head_dim + dim] = __float2bfloat16_rn(acc / total);
+}
+
 __device__ int g_error;
 
 template <int D>
@@ -461,9 +520,15 @@ int launch(const CUtensorMap* k_map, const CUtensorMap* v_map, const __nv_bfloat
                                  max_blocks, out, part_o, part_ml, heads, kv_heads, splits,
                                  scale * 1.4426950408889634f, window, error, cos_t,
                                  sin_t, k_out, v_out);
-  if (status == 0 && splits > 1)
+  const int fold_groups = min(kFoldGroups, (splits + 15) / 16);
+  if (status == 0 && splits > 1 && fold_groups == 1)
     status = launch_overlapped(combine_kernel, dim3(sequences * heads), dim3(D <= 128 ? D : 128),
                                0, stream, 1, (const float*)part_o, (const float*)part_ml, out,
+                               splits, D);
+  else if (status == 0 && splits > 1)
+    status = launch_overlapped(combine_groups_kernel, dim3(sequences * heads),
+                               dim3(D * fold_groups), (fold_groups - 1) * D * sizeof(float3),
+                               stream, 1, (const float*)part_o, (const float*)part_ml, out,
                                splits, D);
   return status;
 }

@@ -374,7 +374,7 @@ def sequence_kv(cache, table_row, length):
 @pytest.mark.parametrize("heads,kv_heads,d,window", [(12, 2, 128, None), (4, 4, 64, None),
                                                      (16, 1, 128, None), (6, 3, 64, 100),
                                                      (14, 2, 128, 64), (5, 5, 128, 1)])
-@pytest.mark.parametrize("splits", [1, 3, None])
+@pytest.mark.parametrize("splits", [1, 3, 20, 33, 64, None])      # 20 and more: the fold in groups
 def test_attention_decode_kernel(heads, kv_heads, d, window, splits):
     rng = np.random.default_rng(heads * d + (window or 0))
     lengths = [1, 63, 64, 65, 700, 2048, 129]
