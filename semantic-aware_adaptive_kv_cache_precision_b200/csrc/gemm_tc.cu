@@ -33,7 +33,7 @@ namespace {
 
 constexpr int BM = 128;          // weight rows per block (MMA M)
 constexpr int BK = 64;           // columns per stage (one 128-byte swizzle row)
-constexpr int kThreads = 192;
+constexpr int kThreads = 224;      // warps: 0 TMA, 1 and 6 MMA issue, 2..5 epilogue
 constexpr int kWTile = BM * BK * 2;
 constexpr int kMaxSplits = 8;     // portable cluster size
 
@@ -74,8 +74,9 @@ struct Cfg {
     return s < 2 ? 2 : s;
   }
   static int smem_bytes(int stages) { return stages * kStageBytes + 1024 + 256; }
-  static constexpr int kTmemCols = kAcc <= 32 ? 32 : kAcc <= 64 ? 64 : kAcc <= 128 ? 128
-                                   : kAcc <= 256 ? 256 : 512;
+  // two accumulators of kAcc columns: the K steps go to them in turn (see the MMA lanes)
+  static constexpr int kTmemCols = 2 * kAcc <= 32 ? 32 : 2 * kAcc <= 64 ? 64 : 2 * kAcc <= 128 ? 128
+                                   : 2 * kAcc <= 256 ? 256 : 512;
 };
 
 __device__ __forceinline__ void cluster_sync_all() {
@@ -280,7 +281,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
       tma::mbar_init(&full[s], 1);
       tma::mbar_init(&empty[s], 1);
     }
-    tma::mbar_init(accum, 1);
+    tma::mbar_init(accum, n_kb > 1 ? 2 : 1);     // one arrival per MMA lane that has work
     tma::fence_barrier_init();
   }
   if (warp == 1) tc::tmem_alloc(tmem_slot, C::kTmemCols);
@@ -297,7 +298,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
   // barrier, where the fetch was 0.5 us of the QKV product's 4.7 us.
   float bias = 0.f;
   float4 bias4 = make_float4(0.f, 0.f, 0.f, 0.f);
-  if (warp >= 2 && k_part == 0 && p.bias) {
+  if (warp >= 2 && warp < 6 && k_part == 0 && p.bias) {
     bias = bias_at(p, n0 + (warp & 3) * 32 + lane);
     if (MT >= 32 && p.splits > 1) {
       const int q = n0 + ((threadIdx.x - 64) & 31) * 4;
@@ -341,13 +342,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
         }
       }
     }
-  } else if (warp == 1) {
-    // ---- MMA issue ------------------------------------------------------------------
-    if (lane == 0) {
+  } else if (warp == 1 || warp == 6) {
+    // ---- MMA issue, by two lanes ------------------------------------------------------
+    // A lane's turn costs it a barrier wait (some 300 cycles even when the tile is there),
+    // its products (45 cycles each at 16 tokens, and the lane is held while they queue) and
+    // a commit (75): one lane alone leaves the tensor pipe idle half of the time. So lane 0
+    // of warp 1 takes the even K steps into one accumulator and lane 0 of warp 6 the odd
+    // ones into a second, and one waits while the other's products run; the epilogue adds
+    // the two accumulators, always in that order.
+    const int which = warp == 1 ? 0 : 1;
+    if (lane == 0 && which < n_kb) {
       constexpr uint32_t idesc = tc::idesc_bf16_f32(BM, MT);
+      const uint32_t acc = tmem + which * C::kAcc;
       bool ok = true;
-      int stage = 0, phase = 0;
-      for (int i = 0; i < n_kb && ok; ++i) {
+      int stage = which % stages, phase = (which / stages) & 1;   // (stages >= 2)
+      for (int i = which; i < n_kb && ok; i += 2) {
         ok = tma::mbar_wait(&full[stage], phase, p.error, 302);
         if (!ok) break;
         tc::fence_after_sync();
@@ -356,20 +365,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
 #pragma unroll
         for (int k = 0; k < BK / 16; ++k) {
           const uint64_t bd = tc::smem_desc_k_major_sw128(b + k * 32);
-          tc::mma_ss(tmem, tc::smem_desc_k_major_sw128(a + k * 32), bd, idesc, i > 0 || k > 0);
+          tc::mma_ss(acc, tc::smem_desc_k_major_sw128(a + k * 32), bd, idesc, i > which || k > 0);
           if (kDual)
-            tc::mma_ss(tmem + MT, tc::smem_desc_k_major_sw128(a + kWTile + k * 32), bd, idesc,
-                       i > 0 || k > 0);
+            tc::mma_ss(acc + MT, tc::smem_desc_k_major_sw128(a + kWTile + k * 32), bd, idesc,
+                       i > which || k > 0);
         }
         tc::commit(&empty[stage]);      // the stage is free once these MMAs have read it
-        if (++stage == stages) {
-          stage = 0;
+        stage += 2;
+        if (stage >= stages) {
+          stage -= stages;
           phase ^= 1;
         }
       }
-      tc::commit(accum);                // the accumulator is complete
+      tc::commit(accum);                // this lane's accumulator is complete
     }
-  } else {
+  } else if (warp < 6) {
     // ---- epilogue: warp w reads the lanes of quarter w % 4 ------------------------------
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;          // lane of tensor memory = weight row in the tile
@@ -378,13 +388,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
     const bool ok = tma::mbar_wait(accum, 0, p.error, 303);
     tc::fence_after_sync();
     const uint32_t taddr = tmem + (static_cast<uint32_t>(quarter * 32) << 16);
+    // sixteen columns of the even K steps' accumulator plus, if any step was odd, the other's
+    const bool two = n_kb > 1;
+    auto columns = [&](int c, float (&v)[16]) {
+      tc::ld_32x32b_x16(taddr + c, v);
+      if (two) {
+        float w[16];
+        tc::ld_32x32b_x16(taddr + C::kAcc + c, w);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) v[j] += w[j];
+      }
+    };
     if (p.splits == 1) {
       if (ok) {
 #pragma unroll 1
         for (int c = 0; c < MT; c += 16) {
           float v[16], u[16];
-          tc::ld_32x32b_x16(taddr + c, v);
-          if (kDual) tc::ld_32x32b_x16(taddr + MT + c, u);
+          columns(c, v);
+          if (kDual) columns(MT + c, u);
 #pragma unroll
           for (int j = 0; j < 16; ++j)
             finish<kEpi>(p, k_part, m0 + c + j, n, v[j], kDual ? u[j] : 0.f, bias);
@@ -396,7 +417,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
 #pragma unroll 1
       for (int c = 0; c < C::kAcc; c += 16) {
         float v[16];
-        tc::ld_32x32b_x16(taddr + c, v);
+        columns(c, v);
 #pragma unroll
         for (int j = 0; j < 16; ++j) mine[(c + j) * BM + row] = v[j];
       }
@@ -406,7 +427,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
   if (p.splits > 1) {
     // Every thread of every block of the cluster comes here, whatever happened above.
     cluster_sync_all();
-    if (warp >= 2) {
+    if (warp >= 2 && warp < 6) {
       const int row = (warp & 3) * 32 + lane;
       const int n = n0 + row;
       const uint32_t base = tma::smem_u32(smem);
