@@ -22,8 +22,9 @@
 // and each block then finishes a share of the token columns by adding the partials of
 // all blocks in rank order (the same order every time) through distributed shared
 // memory. Nothing goes through global scratch. The reference calls cuBLAS for all of
-// this (`src/core_kernels/linear.cu:85-142`); warps: 0 = TMA, 1 = MMA issue and tensor
-// memory, 2..5 = epilogue. TMA loads are plain per-block loads, never cluster multicast.
+// this (`src/core_kernels/linear.cu:85-142`); warps: 0 = TMA, 1 = MMA issue (even K steps)
+// and tensor memory, 6 = MMA issue (odd K steps, into an accumulator of its own), 2..5 =
+// epilogue. TMA loads are plain per-block loads, never cluster multicast.
 #include "common.cuh"
 #include "mma.cuh"
 #include "tcgen05.cuh"
