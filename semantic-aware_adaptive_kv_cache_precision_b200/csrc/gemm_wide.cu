@@ -3,9 +3,9 @@
 //
 //   out[m, n] = silu(x W_gate^T)[m, n] * (x W_up^T)[m, n]          bf16
 //
-// (Measured at 2,048 tokens, 1536 -> 2 x 8960: 86.5 us against 92.4 us for the library's
-// product followed by the activation kernel; at 8,192 tokens 335 against 382 us, 1.35
-// PFLOP/s. The same kernel without the activation loses to the library on the other
+// (Measured at 2,048 tokens, 1536 -> 2 x 8960: 84.1 us against 91.5 us for the library's
+// product followed by the activation kernel; at 8,192 tokens 330 against 377 us, 1.37
+// PFLOP/s, which is what the library's own products sustain under the power cap. The same kernel without the activation loses to the library on the other
 // projections, whose few tiles of 256 x 256 leave SMs idle, so it is not offered for them.)
 //
 // Tokens lie on the MMA's 128 rows, weight rows on its columns: one tcgen05.mma is
@@ -20,7 +20,10 @@
 //
 //   warp 0     TMA: per K step of 64 two boxes of x [128 x 64] and two boxes of W [128 x 64]
 //              into a ring of three 64 KB stages (128-byte swizzle),
-//   warp 1     one lane issues every tcgen05.mma and commits stages and accumulators,
+//   warps 1, 10  MMA issue: lane 0 of each takes ONE of the tile's two products through every
+//              stage and commits the stage and its accumulator. (A lane pays a barrier wait of
+//              some 300 cycles a stage before its products, 128 cycles each, may go out; with
+//              one lane for both products the tensor pipe idled a fifth of the time.)
 //   warps 2-9  epilogue, four warps for each of the tile's two products (a warp reaches the
 //              32 lanes of its number modulo 4): thread = token row; reads its gate and up sums
 //              16 at a time, applies silu(g) * u in fp32, stores 32 bytes at a time.
@@ -43,7 +46,7 @@ constexpr int kStages = 3;
 constexpr int kXBytes = kHalves * BM * BK * 2;  // 32 KB: two boxes of 128 tokens
 constexpr int kWBytes = BN * BK * 2;            // 32 KB: two boxes of 128 rows
 constexpr int kStageBytes = kXBytes + kWBytes;  // 64 KB
-constexpr int kThreads = 64 + kHalves * 128;     // TMA, MMA, and four epilogue warps a product
+constexpr int kThreads = 64 + kHalves * 128 + 32;   // TMA, MMA, four epilogue warps a product, MMA
 constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
 constexpr uint32_t kTmemCols = 512;
 
@@ -58,7 +61,7 @@ struct Params {
 
 struct Barriers {
   uint64_t full[kStages], empty[kStages];
-  uint64_t acc_full;                 // both accumulators of a tile are complete
+  uint64_t acc_full[kHalves];        // an accumulator of a tile is complete
   uint64_t acc_empty[kHalves];       // the epilogue has read one of them
   uint32_t tmem;
 };
@@ -77,9 +80,9 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constan
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
       tma::mbar_init(&bar->full[s], 1);
-      tma::mbar_init(&bar->empty[s], 1);
+      tma::mbar_init(&bar->empty[s], kHalves);       // each MMA lane lets go of it
     }
-    tma::mbar_init(&bar->acc_full, 1);
+    for (int i = 0; i < kHalves; ++i) tma::mbar_init(&bar->acc_full[i], 1);
     for (int i = 0; i < kHalves; ++i) tma::mbar_init(&bar->acc_empty[i], 128);
     tma::fence_barrier_init();
   }
@@ -119,10 +122,11 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constan
         }
       }
     }
-  } else if (warp == 1) {
-    // ---- MMA issue ----------------------------------------------------------------------
+  } else if (warp == 1 || warp == 2 + kHalves * 4) {
+    // ---- MMA issue: this lane's product of every tile ------------------------------------
     if (lane == 0) {
       constexpr uint32_t idesc = tc::idesc_bf16_f32(BM, BN);
+      const int h = warp == 1 ? 0 : 1;
       int stage = 0, phase = 0, round = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++round) {
@@ -131,33 +135,29 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constan
             ok = false;
             break;
           }
-          tc::fence_after_sync();
-          const uint32_t x0 = tma::smem_u32(smem + stage * kStageBytes);
-          const uint32_t b = x0 + kXBytes;
-          for (int h = 0; h < kHalves; ++h) {
-            // an accumulator may be written again once the epilogue has read the last tile's
-            if (kb == 0 && round >= 1 &&
-                !tma::mbar_wait(&bar->acc_empty[h], (round - 1) & 1, p.error, 602)) {
-              ok = false;
-              break;
-            }
-            if (kb == 0) tc::fence_after_sync();
-            const uint32_t a = x0 + h * (kXBytes / kHalves);
-#pragma unroll
-            for (int k = 0; k < BK / 16; ++k)
-              tc::mma_ss(tmem + h * BN, tc::smem_desc_k_major_sw128(a + k * 32),
-                         tc::smem_desc_k_major_sw128(b + k * 32), idesc, kb > 0 || k > 0);
+          // the accumulator may be written again once the epilogue has read the last tile's
+          if (kb == 0 && round >= 1 &&
+              !tma::mbar_wait(&bar->acc_empty[h], (round - 1) & 1, p.error, 602)) {
+            ok = false;
+            break;
           }
+          tc::fence_after_sync();
+          const uint32_t a = tma::smem_u32(smem + stage * kStageBytes) + h * (kXBytes / kHalves);
+          const uint32_t b = tma::smem_u32(smem + stage * kStageBytes) + kXBytes;
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k)
+            tc::mma_ss(tmem + h * BN, tc::smem_desc_k_major_sw128(a + k * 32),
+                       tc::smem_desc_k_major_sw128(b + k * 32), idesc, kb > 0 || k > 0);
           tc::commit(&bar->empty[stage]);
           if (++stage == kStages) {
             stage = 0;
             phase ^= 1;
           }
         }
-        if (ok) tc::commit(&bar->acc_full);
+        if (ok) tc::commit(&bar->acc_full[h]);
       }
     }
-  } else {
+  } else if (warp >= 2) {
     // ---- epilogue: thread = token row ---------------------------------------------------
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;
@@ -166,10 +166,10 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constan
     bool ok = true;
     for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++round) {
       const int m_tile = tile % p.m_tiles, n_tile = tile / p.m_tiles;
-      ok = ok && tma::mbar_wait(&bar->acc_full, round & 1, p.error, 604);
+      const int h = (warp - 2) >> 2;              // which of the tile's two products
+      ok = ok && tma::mbar_wait(&bar->acc_full[h], round & 1, p.error, 604);
       tc::fence_after_sync();
       {
-        const int h = (warp - 2) >> 2;            // which of the tile's two products
         const int m = (m_tile * kHalves + h) * BM + row;
         const uint32_t acc = lane_base + h * BN;
         const int n0 = n_tile * 128;
