@@ -70,6 +70,8 @@ struct Cfg {
                        : MT <= 32 ? (kDual ? 104 : 72) * 1024
                        : MT == 64 ? (kDual ? 160 : 100) * 1024 : 200 * 1024;
     int s = budget / kStageBytes;
+    // (an even ring gives the two MMA lanes, which own the even and the odd stages, equal shares)
+    if (blocks <= 148 && (s & 1) && smem_bytes(s + 1) <= 227 * 1024) ++s;
     if (s > kMaxStages) s = kMaxStages;
     while (s * kStageBytes < kPartialBytes) ++s;
     return s < 2 ? 2 : s;
@@ -348,33 +350,44 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
     // A lane's turn costs it a barrier wait (some 300 cycles even when the tile is there),
     // its products (45 cycles each at 16 tokens, and the lane is held while they queue) and
     // a commit (75): one lane alone leaves the tensor pipe idle half of the time. So lane 0
-    // of warp 1 takes the even K steps into one accumulator and lane 0 of warp 6 the odd
-    // ones into a second, and one waits while the other's products run; the epilogue adds
-    // the two accumulators, always in that order.
+    // of warp 1 takes the K steps that fall into the even STAGES of the ring, into one
+    // accumulator, and lane 0 of warp 6 those of the odd stages, into a second; one waits
+    // while the other's products run, and the epilogue adds the two accumulators, always in
+    // that order.
+    //
+    // A stage belongs to one lane for good. (Dealing out the K steps in turn did not: with
+    // an odd number of stages a lane then came to a stage whose last tile was the other
+    // lane's, could get there before that tile had even landed, and a wait for the parity
+    // after a phase that has not completed is true at once. The lane read a half-filled
+    // tile, freed it a second time, and the ring's phases fell apart: `unspecified launch
+    // failure` on the shapes with long K loops.) A lane waits for each phase of its own
+    // stages in turn, so it can never be more than one phase ahead of a barrier.
     const int which = warp == 1 ? 0 : 1;
     if (lane == 0 && which < n_kb) {
       constexpr uint32_t idesc = tc::idesc_bf16_f32(BM, MT);
       const uint32_t acc = tmem + which * C::kAcc;
-      bool ok = true;
-      int stage = which % stages, phase = (which / stages) & 1;   // (stages >= 2)
-      for (int i = which; i < n_kb && ok; i += 2) {
-        ok = tma::mbar_wait(&full[stage], phase, p.error, 302);
-        if (!ok) break;
-        tc::fence_after_sync();
-        const uint32_t a = tma::smem_u32(smem + stage * C::kStageBytes);
-        const uint32_t b = a + (kDual ? 2 : 1) * kWTile;
+      bool ok = true, fresh = true;     // fresh: this lane's accumulator holds nothing yet
+      int stage = 0, phase = 0;
+      for (int i = 0; i < n_kb && ok; ++i) {
+        if ((stage & 1) == which) {
+          ok = tma::mbar_wait(&full[stage], phase, p.error, 302);
+          if (!ok) break;
+          tc::fence_after_sync();
+          const uint32_t a = tma::smem_u32(smem + stage * C::kStageBytes);
+          const uint32_t b = a + (kDual ? 2 : 1) * kWTile;
 #pragma unroll
-        for (int k = 0; k < BK / 16; ++k) {
-          const uint64_t bd = tc::smem_desc_k_major_sw128(b + k * 32);
-          tc::mma_ss(acc, tc::smem_desc_k_major_sw128(a + k * 32), bd, idesc, i > which || k > 0);
-          if (kDual)
-            tc::mma_ss(acc + MT, tc::smem_desc_k_major_sw128(a + kWTile + k * 32), bd, idesc,
-                       i > which || k > 0);
+          for (int k = 0; k < BK / 16; ++k) {
+            const uint64_t bd = tc::smem_desc_k_major_sw128(b + k * 32);
+            tc::mma_ss(acc, tc::smem_desc_k_major_sw128(a + k * 32), bd, idesc, !fresh || k > 0);
+            if (kDual)
+              tc::mma_ss(acc + MT, tc::smem_desc_k_major_sw128(a + kWTile + k * 32), bd, idesc,
+                         !fresh || k > 0);
+          }
+          fresh = false;
+          tc::commit(&empty[stage]);    // the stage is free once these MMAs have read it
         }
-        tc::commit(&empty[stage]);      // the stage is free once these MMAs have read it
-        stage += 2;
-        if (stage >= stages) {
-          stage -= stages;
+        if (++stage == stages) {
+          stage = 0;
           phase ^= 1;
         }
       }
