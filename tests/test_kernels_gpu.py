@@ -642,6 +642,30 @@ def test_gemm_tc_gated(M, I, K):
     assert np.abs(host(got) - host(two_step)).max() <= 2.0 ** -6 * np.abs(want).max() + 1e-3
 
 
+def test_gemm_tc_long_k_loops_many_times():
+    """Products whose blocks walk the ring of stages many times (56 and 60 K steps a block,
+    as the 7B shape's), launched back to back: every launch gives the same bits, and they
+    are right. (The two MMA lanes once shared stages of an odd ring; a lane that ran ahead
+    then read a tile that had not landed.)"""
+    rng = np.random.default_rng(11)
+    M, H, I = 8, 3584, 18944
+    x = dev(rng.standard_normal((M, H)) * 0.5, torch.bfloat16)
+    w = dev(rng.standard_normal((2 * I, H)) * 0.05, torch.bfloat16)
+    first = ops.gated_up(x, w)
+    for _ in range(30):
+        assert torch.equal(ops.gated_up(x, w), first)
+    g = host(x) @ host(w[:I]).T
+    u = host(x) @ host(w[I:]).T
+    want = g / (1 + np.exp(-g)) * u
+    assert np.abs(host(first) - want).max() <= 2.0 ** -7 * np.abs(want).max() + 1e-3
+    xd = dev(rng.standard_normal((M, I)) * 0.5, torch.bfloat16)
+    wd = dev(rng.standard_normal((H, I)) * 0.02, torch.bfloat16)
+    sums = [ops.linear(xd, wd, out_dtype=torch.float32) for _ in range(30)]
+    assert all(torch.equal(y, sums[0]) for y in sums)
+    np.testing.assert_allclose(host(sums[0]), host(xd) @ host(wd).T, rtol=0, atol=2e-3)
+    assert all(v == 0 for v in ops.kernel_errors().values())
+
+
 def test_gemm_tc_refuses_what_it_cannot_take():
     from semantic_aware_adaptive_kv_cache_precision_b200.ops import gemm_tc
     x = torch.zeros((4, 36), dtype=torch.bfloat16, device=DEV)        # K not a multiple of 8
