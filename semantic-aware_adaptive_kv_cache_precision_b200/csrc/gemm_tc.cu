@@ -22,9 +22,9 @@
 // and each block then finishes a share of the token columns by adding the partials of
 // all blocks in rank order (the same order every time) through distributed shared
 // memory. Nothing goes through global scratch. The reference calls cuBLAS for all of
-// this (`src/core_kernels/linear.cu:85-142`); warps: 0 = TMA, 1 = MMA issue (even K steps)
-// and tensor memory, 6 = MMA issue (odd K steps, into an accumulator of its own), 2..5 =
-// epilogue. TMA loads are plain per-block loads, never cluster multicast.
+// this (`src/core_kernels/linear.cu:85-142`); warps: 0 = TMA, 1 = MMA issue (the ring's even
+// stages) and tensor memory, 6 = MMA issue (the odd stages, into an accumulator of its own),
+// 2..5 = epilogue. TMA loads are plain per-block loads, never cluster multicast.
 #include "common.cuh"
 #include "mma.cuh"
 #include "tcgen05.cuh"
@@ -402,7 +402,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
     const bool ok = tma::mbar_wait(accum, 0, p.error, 303);
     tc::fence_after_sync();
     const uint32_t taddr = tmem + (static_cast<uint32_t>(quarter * 32) << 16);
-    // sixteen columns of the even K steps' accumulator plus, if any step was odd, the other's
+    // sixteen columns of the first lane's accumulator plus, if the second had a K step, its own
     const bool two = n_kb > 1;
     auto columns = [&](int c, float (&v)[16]) {
       tc::ld_32x32b_x16(taddr + c, v);
