@@ -524,7 +524,8 @@ def test_tensor_core_attention_finds_one_far_key(kernel):
 
 @pytest.mark.parametrize("M,N,K", [(1, 128, 64), (8, 1536, 1536), (8, 2048, 1536), (16, 70, 72),
                                    (17, 1000, 352), (64, 1536, 8960), (100, 384, 200),
-                                   (256, 640, 1536), (3, 151936 // 8, 256)])
+                                   (256, 640, 1536), (3, 151936 // 8, 256),
+                                   (20, 19200, 1536), (40, 19200, 1536)])   # many waves, odd rings
 @pytest.mark.parametrize("splits", [None, 1, 3, 8])
 def test_gemm_tc_epilogues(M, N, K, splits):
     from semantic_aware_adaptive_kv_cache_precision_b200.ops import gemm_tc
