@@ -488,6 +488,12 @@ int launch(const CUtensorMap* w_map, const CUtensorMap* x_map, Params p, int n_t
   }
   p.stages = C::stages_for((long long)n_tiles * m_tiles * p.splits * p.parts);
   while (C::smem_bytes(p.stages) > 227 * 1024) --p.stages;
+  // The blocks that fit an SM by their shared memory must fit it by their tensor memory too
+  // (512 columns): a block that waits for columns while its cluster waits for it could wait
+  // for ever. A deeper ring makes the block large enough.
+  while ((227 * 1024) / (C::smem_bytes(p.stages) + 1024) * C::kTmemCols > 512 &&
+         C::smem_bytes(p.stages + 1) <= 227 * 1024)
+    ++p.stages;
   // (A block with few K steps still asks for the whole ring: measured, the decode step is
   // 8 % slower when such blocks ask for less, as the blocks of a cluster then share SMs.)
   if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p.error), g_error) != cudaSuccess)
