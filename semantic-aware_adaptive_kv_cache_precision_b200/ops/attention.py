@@ -231,7 +231,7 @@ def kernel_errors() -> dict:
     """Error words left by waits that gave up (0 = none). Synchronises the device."""
     out = {}
     for name in ("sakv_decode_attention_error", "sakv_prefill_attention_error",
-                 "sakv_prefill_attention_tc_error"):
+                 "sakv_prefill_attention_tc_error", "sakv_gemm_tc_error", "sakv_gemm_wide_error"):
         value = ctypes.c_int(0)
         code = plain_function(name)(ctypes.addressof(value))
         out[name] = value.value if code == 0 else -code
