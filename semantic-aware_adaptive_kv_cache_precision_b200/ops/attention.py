@@ -7,6 +7,7 @@ import ctypes
 
 import torch
 
+from . import _lib
 from ._lib import CACHE_BLOCK, KernelError, call, plain_function, ptr, require_cuda
 
 SM_COUNT = 148
@@ -87,6 +88,8 @@ def attention_decode(qkv: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Te
          ptr(part_o), ptr(part_ml), sequences, heads, kv_heads, head_dim, splits, float(scale),
          int(window) if window else 0, *_rotary_arguments(rotary, write_cache, qkv, k_cache, v_cache,
                                                          heads, kv_heads, head_dim, max_len))
+    if splits > 1:
+        _lib.launches += 1          # the call launched the fold kernel too
     return out
 
 
@@ -224,6 +227,8 @@ def attention_prefill_tc(qkv: torch.Tensor, k_cache: torch.Tensor, v_cache: torc
          ptr(work), work.shape[0], ptr(folds) if n_folds else None, n_folds, ptr(part_o),
          ptr(part_ml), ptr(seq_lens), ptr(block_table), block_table.shape[1], heads, kv_heads,
          head_dim, float(scale), int(window) if window else 0)
+    if n_folds:
+        _lib.launches += 1          # the call launched the fold kernel too
     return out
 
 
