@@ -17,10 +17,11 @@ from .config import ConfigError, Qwen2Config, config_from_dict, config_from_fold
     known_architectures, register_architecture
 from .weights import WeightError, write_random_model
 from .cache import CacheFull
+from .errors import OutOfDeviceMemory
 from .engine import COMPLETE, DECODING, EXHAUSTED, PREFILLING, Ending, Engine
 
 __version__ = "0.1.0"
 
 __all__ = ["ConfigError", "Qwen2Config", "config_from_dict", "config_from_folder",
            "known_architectures", "register_architecture", "WeightError", "write_random_model",
-           "CacheFull", "COMPLETE", "DECODING", "EXHAUSTED", "PREFILLING", "Ending", "Engine"]
+           "CacheFull", "OutOfDeviceMemory", "COMPLETE", "DECODING", "EXHAUSTED", "PREFILLING", "Ending", "Engine"]

@@ -3,9 +3,9 @@
 Every live sequence holds a slot. Cache entries (one per layer call that writes
 a cache) are sorted into groups by what they need:
 
-* entries with the same `KVNeed` (heads, head size, window) form a KV group with
-  storage of its own: `keys`/`values` of shape [entries, blocks, kv_heads, 64,
-  head_dim], a pool of blocks, and for every slot the list of blocks that hold
+* entries with the same `KVNeed` (heads, key and value widths, window, type) form a KV
+  group with storage of its own: `keys` [entries, blocks, kv_heads, 64, head_dim] and
+  `values` [..., value_dim], a pool of blocks, and for every slot the list of blocks that hold
   its positions 0-63, 64-127, ... A group with a window gives a sequence's
   blocks back as soon as every position in them has fallen out of the window.
 * every entry with a `StateNeed` has a tensor [slots, *shape]: state of fixed
@@ -25,6 +25,7 @@ from dataclasses import dataclass
 import numpy as np
 import torch
 
+from ..errors import allocate
 from .allocator import CacheFull, Pool
 from .needs import KVNeed, StateNeed
 
@@ -38,7 +39,7 @@ class EntryView:
     """What one layer call sees of the cache during a step."""
     need: object
     keys: torch.Tensor | None = None          # [blocks, kv_heads, 64, head_dim]
-    values: torch.Tensor | None = None
+    values: torch.Tensor | None = None        # [blocks, kv_heads, 64, value_dim]; None if 0
     block_table: torch.Tensor | None = None   # int32 [B, max_blocks], this step's sequences
     state: torch.Tensor | None = None         # [slots, *shape]; index with the step's slots
     group: int = -1
@@ -49,9 +50,20 @@ class KVGroup:
                  max_slots: int, dtype: torch.dtype, device):
         self.need, self.entries = need, entries
         self.pool = Pool(blocks, "cache block")
-        shape = (len(entries), max(blocks, 1), need.kv_heads, BLOCK, need.head_dim)
-        self.keys = torch.zeros(shape, dtype=dtype, device=device)
-        self.values = torch.zeros(shape, dtype=dtype, device=device)
+        if need.dtype is not None:
+            if need.dtype not in _DTYPES:
+                raise TypeError(f"{need!r}: dtype must be one of {sorted(_DTYPES)} or None")
+            dtype = _DTYPES[need.dtype]
+        lead = (len(entries), max(blocks, 1), need.kv_heads, BLOCK)
+        def zeros(width):
+            shape = lead + (width,)
+            count = int(np.prod(shape))
+            return allocate(lambda: torch.zeros(shape, dtype=dtype, device=device),
+                            f"a cache of {blocks} blocks of {BLOCK} positions for "
+                            f"{len(entries)} layer(s)", count * dtype.itemsize)
+
+        self.keys = zeros(need.head_dim)
+        self.values = None if need.value_width == 0 else zeros(need.value_width)
         self.max_blocks_per_seq = max_blocks_per_seq
         # host copy of every slot's block list; -1 = no block
         self.tables = np.full((max_slots, max_blocks_per_seq), -1, dtype=np.int32)
@@ -82,8 +94,11 @@ class SequenceCache:
             if isinstance(need, KVNeed):
                 by_need.setdefault(need, []).append(entry)
             elif isinstance(need, StateNeed):
-                self.states[entry] = torch.zeros((self.max_slots,) + tuple(need.shape),
-                                                 dtype=_DTYPES[need.dtype], device=device)
+                shape = (self.max_slots,) + tuple(need.shape)
+                self.states[entry] = allocate(
+                    lambda: torch.zeros(shape, dtype=_DTYPES[need.dtype], device=device),
+                    f"the per-sequence state of cache entry {entry}",
+                    int(np.prod(shape)) * _DTYPES[need.dtype].itemsize)
             elif need is not None:
                 raise TypeError(f"cache entry {entry}: unknown need {need!r}")
         for need, entries in by_need.items():
@@ -99,7 +114,8 @@ class SequenceCache:
 
     @property
     def nbytes(self) -> int:
-        total = sum(g.keys.numel() * g.keys.element_size() * 2 for g in self.groups)
+        total = sum(t.numel() * t.element_size() for g in self.groups
+                    for t in (g.keys, g.values) if t is not None)
         return total + sum(s.numel() * s.element_size() for s in self.states.values())
 
     # -- slots --------------------------------------------------------------
@@ -138,7 +154,8 @@ class SequenceCache:
         if self.poison_freed and group.keys.is_floating_point():
             index = torch.as_tensor(blocks, dtype=torch.long, device=self.device)
             group.keys.index_fill_(1, index, float("nan"))
-            group.values.index_fill_(1, index, float("nan"))
+            if group.values is not None:
+                group.values.index_fill_(1, index, float("nan"))
         group.pool.give_back(blocks)
 
     # -- growth -------------------------------------------------------------
@@ -199,7 +216,9 @@ class SequenceCache:
         if isinstance(need, KVNeed):
             g, i = self.entry_group[entry]
             group = self.groups[g]
-            return EntryView(need, group.keys[i], group.values[i], device_tables[g], None, g)
+            return EntryView(need, group.keys[i],
+                             None if group.values is None else group.values[i],
+                             device_tables[g], None, g)
         if isinstance(need, StateNeed):
             return EntryView(need, state=self.states[entry])
         return EntryView(need)

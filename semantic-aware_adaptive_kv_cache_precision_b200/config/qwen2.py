@@ -168,7 +168,9 @@ class Qwen2Config:
             run_order=tuple(LayerCall(block=i, cache=i) for i in range(self.num_hidden_layers)),
             final_norm=norm, tie_head=self.tie_word_embeddings,
             max_positions=self.max_position_embeddings, stop_token_ids=self.eos_token_id,
-            stored_dtype=self.torch_dtype, init_std=self.initializer_range)
+            stored_dtype=self.torch_dtype, init_std=self.initializer_range,
+            # exporters of this architecture have written the rotary table's frequencies
+            ignore_tensors=("*.rotary_emb.inv_freq",))
 
 
 register_architecture(Qwen2Config.architecture, Qwen2Config)

@@ -15,7 +15,7 @@ here needs to change for it.
 
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Optional
 
 
@@ -104,6 +104,12 @@ class LayerCall:
 
 @dataclass(frozen=True)
 class ModelSpec:
+    """`embed_scale` multiplies the embedding's rows as they enter the residual stream;
+    `logit_scale` multiplies the logits and `logit_softcap` c then bends them to
+    `c * tanh(logits / c)` (None: neither); `head_bias_name` names a bias [vocab] of the
+    output head. `ignore_tensors`: shell-style patterns of tensor names that a checkpoint
+    of this architecture may hold without any part reading them (buffers that exporters
+    write, such as a rotary table's `inv_freq`); anything else unexpected is an error."""
     architecture: str
     vocab_size: int
     hidden: int
@@ -118,7 +124,11 @@ class ModelSpec:
     stop_token_ids: tuple = ()
     stored_dtype: str = "bfloat16"
     init_std: float = 0.02
-    extra: dict = field(default_factory=dict, compare=False)
+    embed_scale: float = 1.0
+    logit_scale: float = 1.0
+    logit_softcap: Optional[float] = None
+    head_bias_name: Optional[str] = None
+    ignore_tensors: tuple = ()
 
     def cache_entries(self) -> int:
         return 1 + max((c.cache for c in self.run_order), default=-1)

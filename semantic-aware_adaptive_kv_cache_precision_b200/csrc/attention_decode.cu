@@ -45,7 +45,8 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap k_map,
                         float* __restrict__ part_ml, int heads, int kv_heads, int splits,
                         float scale_log2e, int window, int* __restrict__ error,
                         const float* __restrict__ cos_t, const float* __restrict__ sin_t,
-                        __nv_bfloat16* __restrict__ k_out, __nv_bfloat16* __restrict__ v_out) {
+                        int rotary_rows, __nv_bfloat16* __restrict__ k_out,
+                        __nv_bfloat16* __restrict__ v_out) {
   // With `cos_t`/`sin_t` (rotary tables [positions, D / 2], rotation over the whole head) the
   // queries, keys and values in `q`'s rows are as the projection left them: this kernel
   // rotates its queries as it loads them, and the one block of a (sequence, KV head) whose
@@ -78,7 +79,10 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap k_map,
   // started, and every cached key but the newest was written by an earlier step: all of
   // that is read, and those tiles are on their way, before this kernel waits for the one
   // before it, which wrote the queries and the newest key and value.
-  const int kv_len = seq_lens[b];
+  // (a length outside [0, max_blocks * 64] cannot come from the engine; a caller of the
+  // exported function that passes one gets zeros for that sequence, not a wild read)
+  const int given_len = seq_lens[b];
+  const int kv_len = given_len < 0 || given_len > max_blocks * KT ? 0 : given_len;
   const int first_key = (window > 0 && kv_len - window > 0) ? kv_len - window : 0;
   const int first_tile = first_key / KT;
   const int n_tiles = (kv_len + KT - 1) / KT;
@@ -110,14 +114,17 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap k_map,
   const int newest = n_tiles - 1 - t0;         // the tile that holds the newest key, if in this split
   // (when this kernel itself writes the newest key, nobody before it does: every tile early)
   const bool fused = cos_t != nullptr;
-  const bool writes = fused && k_out != nullptr && newest >= 0 && newest < n_key_tiles;
+  const bool writes = fused && k_out != nullptr && newest >= 0 && newest < n_key_tiles &&
+                      kv_len > 0 && kv_len - 1 < rotary_rows;
   if (threadIdx.x == 0)
     for (int i = 0; i < min(kStages, n_key_tiles); ++i)
       if (i != newest || (fused && k_out != nullptr)) request(i, false);
   if (threadIdx.x < n_key_tiles)
     listed[threadIdx.x] = block_table[(long long)b * max_blocks + t0 + threadIdx.x];
   // rotary factors of this sequence's newest position, for the columns this lane holds
-  const int pos = kv_len - 1;
+  // (clamped into the tables: a position they do not hold is the caller's fault, but is not
+  // read from beyond them)
+  const int pos = min(max(kv_len - 1, 0), max(rotary_rows - 1, 0));
   constexpr int HS = D / 32;                     // k-steps of 16 in half a head
   float2 cs[HS][2], sn[HS][2];
   if (fused) {
@@ -375,9 +382,10 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap k_map,
         acc.z += weight[w] * v.z; acc.w += weight[w] * v.w;
       }
       if (splits == 1) {
+        const float inv = total > 0.f ? 1.f / total : 0.f;      // no key at all: zeros
         *reinterpret_cast<uint2*>(out + ((long long)b * heads + h) * D + lane * 4) =
-            make_uint2(mma::pack_bf16(acc.x / total, acc.y / total),
-                       mma::pack_bf16(acc.z / total, acc.w / total));
+            make_uint2(mma::pack_bf16(acc.x * inv, acc.y * inv),
+                       mma::pack_bf16(acc.z * inv, acc.w * inv));
       } else {
         *reinterpret_cast<float4*>(part_o + (((long long)b * heads + h) * splits + split) * D +
                                    lane * 4) = acc;
@@ -428,7 +436,7 @@ __global__ void combine_kernel(const float* __restrict__ part_o, const float* __
         acc += w * o[j];
       }
     }
-    out[bh * head_dim + dim] = __float2bfloat16_rn(acc / total);
+    out[bh * head_dim + dim] = __float2bfloat16_rn(total > 0.f ? acc / total : 0.f);
   }
 }
 
@@ -488,7 +496,7 @@ __global__ void combine_groups_kernel(const float* __restrict__ part_o, const fl
       big = top;
     }
   }
-  out[bh * head_dim + dim] = __float2bfloat16_rn(acc / total);
+  out[bh * head_dim + dim] = __float2bfloat16_rn(total > 0.f ? acc / total : 0.f);
 }
 
 __device__ int g_error;
@@ -498,8 +506,15 @@ int launch(const CUtensorMap* k_map, const CUtensorMap* v_map, const __nv_bfloat
            long long q_stride, const int32_t* seq_lens, const int32_t* block_table, int max_blocks,
            __nv_bfloat16* out, float* part_o, float* part_ml, int sequences, int heads,
            int kv_heads, int splits, float scale, int window, const float* cos_t,
-           const float* sin_t, __nv_bfloat16* k_out, __nv_bfloat16* v_out, cudaStream_t stream) {
-  static bool configured = false;
+           const float* sin_t, int rotary_rows, __nv_bfloat16* k_out, __nv_bfloat16* v_out,
+           cudaStream_t stream) {
+  // a kernel's attributes belong to a device: set once on each device that launches it
+  constexpr int kDevices = 64;
+  static bool configured_on[kDevices] = {};
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess) return cudaErrorInvalidValue;
+  const bool remember = device >= 0 && device < kDevices;
+  const bool configured = remember && configured_on[device];
   int* error = nullptr;
   if (cudaGetSymbolAddress(reinterpret_cast<void**>(&error), g_error) != cudaSuccess)
     return cudaErrorInvalidValue;
@@ -512,14 +527,14 @@ int launch(const CUtensorMap* k_map, const CUtensorMap* v_map, const __nv_bfloat
                                cudaFuncAttributePreferredSharedMemoryCarveout,
                                cudaSharedmemCarveoutMaxShared);
     if (e != cudaSuccess) return static_cast<int>(e);
-    configured = true;
+    if (remember) configured_on[device] = true;
   }
   const dim3 grid(splits, kv_heads, sequences);
   int status = launch_overlapped(decode_attention_kernel<D>, grid, dim3(kThreads), Smem<D>::kBytes,
                                  stream, 1, *k_map, *v_map, q, q_stride, seq_lens, block_table,
                                  max_blocks, out, part_o, part_ml, heads, kv_heads, splits,
                                  scale * 1.4426950408889634f, window, error, cos_t,
-                                 sin_t, k_out, v_out);
+                                 sin_t, rotary_rows, k_out, v_out);
   const int fold_groups = min(kFoldGroups, (splits + 15) / 16);
   if (status == 0 && splits > 1 && fold_groups == 1)
     status = launch_overlapped(combine_kernel, dim3(sequences * heads), dim3(D <= 128 ? D : 128),
@@ -551,13 +566,14 @@ SAKV_EXPORT int sakv_decode_attention(const void* k_map, const void* v_map, cons
                                       float* part_o, float* part_ml, int sequences, int heads,
                                       int kv_heads, int head_dim, int splits, float scale,
                                       int window, const float* cos_table, const float* sin_table,
-                                      void* k_cache, void* v_cache, cudaStream_t stream) {
-  // `cos_table`, `sin_table` (fp32 [positions, head_dim / 2], both or neither): `q`'s rows are
+                                      int rotary_rows, void* k_cache, void* v_cache,
+                                      cudaStream_t stream) {
+  // `cos_table`, `sin_table` (fp32 [rotary_rows, head_dim / 2], both or neither): `q`'s rows are
   // then the projection's whole output [q | k | v], unrotated, and the kernel rotates the
   // queries and, into the cache entry `k_cache`, `v_cache` (or nowhere if those are null),
   // writes the newest position's rotated key and its value.
   if ((cos_table == nullptr) != (sin_table == nullptr) || (k_cache == nullptr) != (v_cache == nullptr) ||
-      (k_cache && !cos_table) || ((uintptr_t)cos_table & 7) || ((uintptr_t)sin_table & 7) ||
+      (k_cache && !cos_table) || (cos_table && rotary_rows <= 0) || ((uintptr_t)cos_table & 7) || ((uintptr_t)sin_table & 7) ||
       ((uintptr_t)k_cache & 15) || ((uintptr_t)v_cache & 15) ||
       (cos_table && (((uintptr_t)q & 15) || (q_stride & 7))))
     return cudaErrorInvalidValue;
@@ -570,7 +586,7 @@ SAKV_EXPORT int sakv_decode_attention(const void* k_map, const void* v_map, cons
   return launch<D>((const CUtensorMap*)k_map, (const CUtensorMap*)v_map,                      \
                    (const __nv_bfloat16*)q, q_stride, seq_lens, block_table, max_blocks,      \
                    (__nv_bfloat16*)out, part_o, part_ml, sequences, heads, kv_heads, splits,  \
-                   scale, window, cos_table, sin_table, (__nv_bfloat16*)k_cache,              \
+                   scale, window, cos_table, sin_table, rotary_rows, (__nv_bfloat16*)k_cache, \
                    (__nv_bfloat16*)v_cache, stream)
   if (head_dim == 64) GO(64);
   if (head_dim == 128) GO(128);
@@ -647,9 +663,9 @@ SAKV_EXPORT int sakv_decode_attention_static_scratch(
     return launch<64>((const CUtensorMap*)k_map, (const CUtensorMap*)v_map,
                       (const __nv_bfloat16*)q, q_stride, seq_lens, block_table, max_blocks,
                       (__nv_bfloat16*)out, part_o, part_ml, sequences, heads, kv_heads, splits,
-                      scale, window, nullptr, nullptr, nullptr, nullptr, stream);
+                      scale, window, nullptr, nullptr, 0, nullptr, nullptr, stream);
   return launch<128>((const CUtensorMap*)k_map, (const CUtensorMap*)v_map,
                      (const __nv_bfloat16*)q, q_stride, seq_lens, block_table, max_blocks,
                      (__nv_bfloat16*)out, part_o, part_ml, sequences, heads, kv_heads, splits,
-                     scale, window, nullptr, nullptr, nullptr, nullptr, stream);
+                     scale, window, nullptr, nullptr, 0, nullptr, nullptr, stream);
 }

@@ -103,7 +103,24 @@ static inline int launch_overlapped(void (*kernel)(KernelArgs...), dim3 grid, di
   return e != cudaSuccess ? static_cast<int>(e) : launch_status();
 }
 
-static inline int grid_for(long long work, int threads, int cap = 148 * 16) {
+// The number of SMs of the current device, asked once per device (148 on a B200; fewer on
+// a part with SMs masked off). Grids and the one-wave reasoning of the launchers use it.
+static inline int sm_count() {
+  constexpr int kDevices = 64;
+  static int known[kDevices] = {};
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kDevices) return 148;
+  if (known[device] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || n <= 0)
+      n = 148;
+    known[device] = n;
+  }
+  return known[device];
+}
+
+static inline int grid_for(long long work, int threads, int per_sm = 16) {
+  const int cap = sm_count() * per_sm;
   long long blocks = (work + threads - 1) / threads;
   if (blocks < 1) blocks = 1;
   if (blocks > cap) blocks = cap;

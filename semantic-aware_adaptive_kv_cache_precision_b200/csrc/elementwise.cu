@@ -93,7 +93,28 @@ __global__ void add_into_kernel(float* __restrict__ acc, const T* __restrict__ y
     acc[i] += widen(y[i]);
 }
 
+// x = x * scale, then (cap > 0) x = cap * tanh(x / cap): an embedding's or a head's scale,
+// and the soft cap some architectures put on their logits. fp32 in place.
+__global__ void scale_cap_kernel(float* __restrict__ x, long long count, float scale, float cap) {
+  let_next_kernel_start();
+  wait_for_previous_kernel();
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < count;
+       i += (long long)gridDim.x * blockDim.x) {
+    float v = x[i] * scale;
+    if (cap > 0.f) v = cap * tanhf(v / cap);
+    x[i] = v;
+  }
+}
+
 }  // namespace
+
+SAKV_EXPORT int sakv_scale_cap(float* x, long long count, float scale, float cap,
+                               cudaStream_t stream) {
+  if (count < 0 || cap < 0.f) return cudaErrorInvalidValue;
+  if (count == 0) return 0;
+  return launch_overlapped(scale_cap_kernel, dim3(grid_for(count, 256)), dim3(256), 0, stream, 1,
+                           x, count, scale, cap);
+}
 
 SAKV_EXPORT int sakv_embed(const int32_t* ids, const void* table, int table_dtype, float* out,
                            int tokens, int hidden, int vocab, cudaStream_t stream) {
@@ -118,7 +139,7 @@ SAKV_EXPORT int sakv_gated_silu(const void* gate_up, void* out, int dtype, int t
   if (dtype == SAKV_BF16 && inter % 8 == 0 && !((uintptr_t)gate_up & 15) && !((uintptr_t)out & 15)) {
     const int across = (inter / 8 + 127) / 128;
     int down = (tokens + 1) / 2;
-    const int most = (148 * 16 + across - 1) / across;
+    const int most = (sm_count() * 16 + across - 1) / across;
     if (down > most) down = most;
     gated_silu_bf16x8_kernel<<<dim3(across, down), 128, 0, stream>>>(
         (const uint4*)gate_up, (uint4*)out, inter / 8, tokens);
@@ -140,7 +161,7 @@ SAKV_EXPORT int sakv_add_into(float* acc, const void* y, int dtype, long long co
   if (count < 0) return cudaErrorInvalidValue;
   if (count == 0) return 0;
   if (dtype == SAKV_F32 && count % 4 == 0 && !((uintptr_t)acc & 15) && !((uintptr_t)y & 15)) {
-    add_into_f32x4_kernel<<<grid_for(count / 4, 256, 148 * 32), 256, 0, stream>>>(
+    add_into_f32x4_kernel<<<grid_for(count / 4, 256, 32), 256, 0, stream>>>(
         (float4*)acc, (const float4*)y, count / 4);
     return launch_status();
   }

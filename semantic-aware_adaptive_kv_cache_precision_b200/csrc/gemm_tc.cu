@@ -16,7 +16,7 @@
 //   gated_silu         : silu(C_gate) * C_up           gate and up rows [n] and [n + I] of one
 //                                                      matrix, two accumulators side by side
 //
-// With few tokens and a small N there are too few row tiles to fill 148 SMs, so K is
+// With few tokens and a small N there are too few row tiles to fill the GPU's SMs, so K is
 // split over the blocks of a thread-block cluster (up to 8, along blockIdx.z): every
 // block leaves its partial tile in its own shared memory, the cluster synchronises,
 // and each block then finishes a share of the token columns by adding the partials of
@@ -66,12 +66,13 @@ struct Cfg {
   // stages as fit, to keep enough bytes in flight; with several waves it takes fewer, so
   // that two or three blocks share an SM and one's epilogue overlaps another's streaming.
   static int stages_for(long long blocks) {
-    const int budget = blocks <= 148 ? 200 * 1024
+    const int sms = sm_count();
+    const int budget = blocks <= sms ? 200 * 1024
                        : MT <= 32 ? (kDual ? 104 : 72) * 1024
                        : MT == 64 ? (kDual ? 160 : 100) * 1024 : 200 * 1024;
     int s = budget / kStageBytes;
     // (an even ring gives the two MMA lanes, which own the even and the odd stages, equal shares)
-    if (blocks <= 148 && (s & 1) && smem_bytes(s + 1) <= 227 * 1024) ++s;
+    if (blocks <= sms && (s & 1) && smem_bytes(s + 1) <= 227 * 1024) ++s;
     if (s > kMaxStages) s = kMaxStages;
     while (s * kStageBytes < kPartialBytes) ++s;
     return s < 2 ? 2 : s;

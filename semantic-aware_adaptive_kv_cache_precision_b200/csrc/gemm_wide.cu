@@ -221,7 +221,7 @@ int launch(const CUtensorMap* x_map, const CUtensorMap* w_map, Params p, cudaStr
   if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p.error), g_error) != cudaSuccess)
     return cudaErrorInvalidValue;
   const int tiles = p.m_tiles * p.n_tiles;
-  const int grid = tiles < 148 ? tiles : 148;
+  const int grid = tiles < sm_count() ? tiles : sm_count();
   gemm_wide_kernel<<<grid, kThreads, kSmemBytes, stream>>>(*x_map, *w_map, p);
   return launch_status();
 }

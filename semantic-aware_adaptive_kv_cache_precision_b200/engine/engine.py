@@ -21,7 +21,8 @@ from ..ops import _lib
 from ..cache import BLOCK, CacheFull, SequenceCache
 from ..config import config_from_dict, config_from_folder
 from .generate import (decode_ahead, COMPLETE, DECODING, EXHAUSTED, PREFILLING, Ending, RequestState,
-                       check_prompt, check_window, plan_batches, plan_prefill, positions_needed)
+                       check_prompt, check_window, plan_batches, plan_prefill, positions_needed,
+                       stop_ids_of_folder)
 from .model import DecoderModel
 from .step import StepStager
 
@@ -80,12 +81,14 @@ class Engine:
         self.ending = None
         self.endings: list = []
         self._loaded = False
+        self._tokenizer = None
 
     # -- loading ----------------------------------------------------------------
 
     def load_weights(self) -> "Engine":
         """Check the checkpoint against the configuration, then put every tensor on
-        the device; a model is never half loaded."""
+        the device; a model is never half loaded. If the device has no room the call
+        raises `OutOfDeviceMemory` and the engine stays as it was before the call."""
         with torch.cuda.device(self.device):
             if self.model_dir is not None:
                 self.model.load(self.model_dir)
@@ -93,6 +96,30 @@ class Engine:
                 self.model.load_random(0 if self.random_seed is None else self.random_seed)
         self._loaded = True
         return self
+
+    def release(self) -> None:
+        """Give up the cache, the graphs that were captured over it and over the weights, and
+        the TMA descriptors that were kept for both (a later tensor at one of their addresses
+        then gets a descriptor of its own). The weights stay; the next step builds a new
+        cache. Called when the engine is dropped."""
+        from .. import ops
+        self._graphs.clear()
+        self._prefill_graphs.clear()
+        held = [] if self.model.arena is None else [self.model.arena.buffer]
+        if self.cache is not None:
+            for group in self.cache.groups:
+                held += [group.keys, group.values]
+        try:
+            ops.forget_descriptors(*held)
+        except Exception:            # the interpreter may be shutting down
+            pass
+        self.cache = None
+
+    def __del__(self):
+        try:
+            self.release()
+        except Exception:
+            pass
 
     def _need_loaded(self) -> None:
         if not self._loaded:
@@ -102,11 +129,14 @@ class Engine:
         if self.cache is None:
             self._need_loaded()
             act = torch.float32 if self.dtype == "float32" else torch.bfloat16
-            self.cache = SequenceCache(self.model.cache_needs(), self.max_tokens,
-                                       self.spec.max_positions, act, self.device,
-                                       max_slots=min(-(-self.max_tokens // BLOCK), 4096),
-                                       poison_freed=self.poison_freed)
-            self.model.prepare(self.cache.max_seq_len)
+            # built whole before the engine keeps it: if the device has no room
+            # (`OutOfDeviceMemory`) the engine still has no cache and can be asked again
+            cache = SequenceCache(self.model.cache_needs(), self.max_tokens,
+                                  self.spec.max_positions, act, self.device,
+                                  max_slots=min(-(-self.max_tokens // BLOCK), 4096),
+                                  poison_freed=self.poison_freed)
+            self.model.prepare(cache.max_seq_len)
+            self.cache = cache
         return self.cache
 
     @property
@@ -117,13 +147,32 @@ class Engine:
     def eos_token_ids(self) -> frozenset:
         """generation_config.json's eos_token_id if the folder has one
         (`src/microinfer/engine.py:1148-1153`), else config.json's."""
-        if self.model_dir is not None:
-            path = self.model_dir / "generation_config.json"
-            if path.is_file():
-                eos = json.loads(path.read_text()).get("eos_token_id")
-                if eos is not None:
-                    return frozenset(eos if isinstance(eos, list) else [eos])
-        return frozenset(self.spec.stop_token_ids)
+        return stop_ids_of_folder(self.model_dir, self.spec.stop_token_ids)
+
+    @property
+    def tokenizer(self):
+        """The model folder's own tokenizer.json through the `tokenizers` package
+        (`src/microinfer/engine.py:1133-1140`). Token ids in and out are the contract of
+        this library; text is a convenience for folders that carry a tokenizer."""
+        if self._tokenizer is None:
+            path = None if self.model_dir is None else self.model_dir / "tokenizer.json"
+            if path is None or not path.is_file():
+                raise RuntimeError("this model has no tokenizer.json: give token ids, not text")
+            try:
+                from tokenizers import Tokenizer
+            except ImportError:
+                raise RuntimeError("the `tokenizers` package is not installed: give token "
+                                   "ids, not text") from None
+            self._tokenizer = Tokenizer.from_file(str(path))
+        return self._tokenizer
+
+    def encode(self, text: str) -> np.ndarray:
+        """Token ids (int32) of `text` (`src/microinfer/engine.py:1142-1143`)."""
+        return np.asarray(self.tokenizer.encode(text).ids, dtype=np.int32)
+
+    def decode(self, token_ids) -> str:
+        """Text of token ids (`src/microinfer/engine.py:1145-1146`)."""
+        return self.tokenizer.decode([int(t) for t in token_ids])
 
     def footprint(self) -> dict:
         """Bytes on the device: weights, cache, and what the device reports."""
@@ -143,7 +192,8 @@ class Engine:
         self._need_cache().close(slots)
 
     def step(self, slots: list, new_tokens: list | None = None, want: list | None = None, *,
-             device_tokens: torch.Tensor | None = None) -> torch.Tensor:
+             device_tokens: torch.Tensor | None = None,
+             hidden_states: list | None = None) -> torch.Tensor:
         """Feed `new_tokens[i]` to the sequence in `slots[i]`, after what its cache
         already holds, all sequences as one batch. Returns fp32 logits
         [wanted, vocab] on the device for `want[i]`, the places among
@@ -152,7 +202,16 @@ class Engine:
 
         `device_tokens` (int32 [len(slots)], on the device) instead of `new_tokens`: one
         token for each sequence, taken from the device on the stream, so that a step can be
-        launched before the host has read the tokens the step before it chose."""
+        launched before the host has read the tokens the step before it chose.
+
+        The sequences of a step need not be at the same place: some may start (a prompt),
+        some go on with a further piece of their prompt, some with one token, all in the one
+        batch.
+
+        `hidden_states` (a list): fp32 copies [tokens, hidden] of the residual stream are
+        appended to it, after the embedding, after every layer call but the last, and after
+        the final norm (the reference's order, `src/microinfer/model.py:355-364, 398-402`);
+        such a step runs kernel by kernel."""
         cache = self._need_cache()
         if device_tokens is not None:
             if new_tokens is not None:
@@ -183,7 +242,12 @@ class Engine:
             cache.reserve(slots, ends)
             ctx = self._stager.build(slots, new_tokens, starts, rows, cache.tables_for(slots),
                                      device_tokens)
-            if self.cuda_graphs and self.model.graph_safe and ctx.is_decode \
+            if hidden_states is not None:
+                x = self.model.hidden(ctx, cache, capture=hidden_states)
+                hidden_states.append(self.model.final_states(x))
+                logits = self.model.logits(x, ctx.want) if rows else torch.empty(
+                    (0, self.spec.vocab_size), dtype=torch.float32, device=self.device)
+            elif self.cuda_graphs and self.model.graph_safe and ctx.is_decode \
                     and rows == list(range(len(slots))):
                 logits = self._decode_by_graph(ctx, cache)
             elif self.cuda_graphs and self.model.graph_safe and 0 < len(rows) <= 64 \
@@ -197,6 +261,17 @@ class Engine:
             cache.advance(slots, ends)
             return logits
 
+    @staticmethod
+    def _slots_in_key(ctx, cache) -> tuple:
+        """What a captured step keeps of the host's view of it. A graph replays the launches
+        it was captured with, Python integers included. Per-sequence state is indexed by slot
+        (`view.state[slot]` with the host's `step.host_slots`), so a graph of a model that
+        has state belongs to the slots it was captured on; keys and values are reached
+        through block lists on the device, so a model without state shares its graphs among
+        all slots. (`step.starts`, `max_position` and `max_len` change from one replay to
+        the next: a part whose launches depend on them is not `graph_safe`.)"""
+        return tuple(ctx.host_slots) if cache.states else ()
+
     def _decode_by_graph(self, ctx, cache) -> torch.Tensor:
         """Run a decode step through the CUDA graph of its shape (batch size and width of
         the block lists), capturing it the first time the shape comes up after one
@@ -204,7 +279,8 @@ class Engine:
         if not self._decode_ran_eagerly:
             self._decode_ran_eagerly = True
             return self.model.logits(self.model.hidden(ctx, cache), ctx.want)
-        key = (ctx.sequences, tuple(tuple(t.shape) for t in ctx.tables), self._stager.generation)
+        key = (ctx.sequences, tuple(tuple(t.shape) for t in ctx.tables), self._stager.generation,
+               self._slots_in_key(ctx, cache))
         entry = self._graphs.get(key)
         if entry is None:
             if len(self._graphs) >= 64:                 # shapes come and go; keep the table small
@@ -244,7 +320,8 @@ class Engine:
         from then on replayed. Launching a prefill's 400 kernels from Python takes 4 to 5 ms,
         longer than a short prompt's kernels run; a replay takes what the kernels take.
         Requests of a shape never seen again cost nothing but a dictionary entry."""
-        key = (shape, tuple(tuple(t.shape) for t in ctx.tables), self._stager.generation)
+        key = (shape, tuple(tuple(t.shape) for t in ctx.tables), self._stager.generation,
+               self._slots_in_key(ctx, cache))
         entry = self._prefill_graphs.get(key)
         if entry is None:                                   # first time: eagerly
             if len(self._prefill_graphs) >= 256:
@@ -284,19 +361,69 @@ class Engine:
 
     # -- whole sequences ---------------------------------------------------------------
 
-    def forward(self, token_ids) -> np.ndarray:
+    def forward(self, token_ids, *, capture_hidden_states: bool = False):
         """fp32 logits (seq, vocab) for every position of one sequence
-        (`src/microinfer/engine.py:1157-1178`)."""
+        (`src/microinfer/engine.py:1157-1178`). With `capture_hidden_states`, returns
+        `(logits, hidden_states)`, the states fp32 (layer calls + 1, seq, hidden): the
+        embedding's output, the stream after every layer call but the last, and the last
+        one's after the final norm."""
         self._need_loaded()
         ids = check_prompt(token_ids, self.spec.vocab_size)
         check_window(len(ids), self.spec.max_positions)
         (slot,) = self.open(1)
         try:
-            out = []
+            out, states = [], []
             for begin in range(0, len(ids), self.max_step_tokens):
                 chunk = ids[begin:begin + self.max_step_tokens]
-                out.append(self.step([slot], [chunk], [list(range(len(chunk)))]).cpu().numpy())
-            return np.concatenate(out)
+                captured = [] if capture_hidden_states else None
+                out.append(self.step([slot], [chunk], [list(range(len(chunk)))],
+                                     hidden_states=captured).cpu().numpy())
+                if capture_hidden_states:
+                    states.append(torch.stack([c.float() for c in captured]).cpu().numpy())
+            logits = np.concatenate(out)
+            if capture_hidden_states:
+                return logits, np.concatenate(states, axis=1)
+            return logits
+        finally:
+            self.close([slot])
+
+    def cached_kv(self, token_ids) -> tuple[np.ndarray, np.ndarray]:
+        """What the cache holds after prefilling one sequence: keys and values, each fp32
+        (cache entries, seq, kv_heads, head_dim), read back from the blocks the sequence was
+        given (`src/microinfer/engine.py:1819-1834`). Keys are as stored: rotated, WITH their
+        projection's bias (the reference caches them without). A position that a windowed
+        entry has already given back reads as NaN; an entry that keeps no keys and values
+        (per-sequence state) is left out. All kept entries must have one shape."""
+        self._need_loaded()
+        ids = check_prompt(token_ids, self.spec.vocab_size)
+        check_window(len(ids), self.spec.max_positions)
+        cache = self._need_cache()
+        (slot,) = self.open(1)
+        try:
+            for begin in range(0, len(ids), self.max_step_tokens):
+                chunk = ids[begin:begin + self.max_step_tokens]
+                self.step([slot], [chunk], [[]])
+            torch.cuda.synchronize(self.device)
+            keys, values = [], []
+            for entry, need in enumerate(cache.needs):
+                if entry not in cache.entry_group:
+                    continue
+                g, i = cache.entry_group[entry]
+                group = cache.groups[g]
+                if group.values is None:
+                    continue
+                blocks = group.tables[slot, :-(-len(ids) // BLOCK)]
+                held = torch.as_tensor(np.maximum(blocks, 0), dtype=torch.long, device=self.device)
+
+                def read(store):
+                    rows = store[i][held].float()                  # [blocks, kv_heads, 64, d]
+                    rows[torch.as_tensor(blocks < 0, device=self.device)] = float("nan")
+                    rows = rows.permute(0, 2, 1, 3).reshape(-1, rows.shape[1], rows.shape[3])
+                    return rows[:len(ids)].cpu().numpy()
+
+                keys.append(read(group.keys))
+                values.append(read(group.values))
+            return np.stack(keys), np.stack(values)
         finally:
             self.close([slot])
 
@@ -304,8 +431,9 @@ class Engine:
 
     def generate(self, prompt, max_new_tokens: int = 64, *, stop_at_eos: bool = True,
                  report=None, temperature: float = 0.0, seed: int = 0, stop_token_ids=None):
-        """New token ids for one prompt (a 1-D sequence of ids: returns one int32
-        array) or for a list of prompts (returns a list of int32 arrays).
+        """New token ids for one prompt (a 1-D sequence of ids, or text if the model folder
+        has a tokenizer.json: returns one int32 array) or for a list of prompts (returns a
+        list of int32 arrays).
 
         Prompts are taken in batches that start together; each batch prefills all
         its prompts in one step and then decodes one token per live request a
@@ -318,8 +446,11 @@ class Engine:
         `self.endings` say how each request ended.
         """
         self._need_loaded()
+        if isinstance(prompt, str):                    # text, if the folder has a tokenizer
+            prompt = self.encode(prompt)
         single = not _is_list_of_sequences(prompt)
         prompts = [prompt] if single else list(prompt)
+        prompts = [self.encode(p) if isinstance(p, str) else p for p in prompts]
         if max_new_tokens < 0:
             raise ValueError(f"max_new_tokens must not be negative, got {max_new_tokens}")
         ids = [check_prompt(p, self.spec.vocab_size, f"prompt {i}" if not single else "token_ids")
@@ -450,5 +581,5 @@ def _is_list_of_sequences(prompt) -> bool:
     if isinstance(prompt, np.ndarray):
         return False              # an array is one prompt; a 2-D one is refused as such
     if isinstance(prompt, (list, tuple)) and prompt:
-        return isinstance(prompt[0], (list, tuple, np.ndarray))
+        return isinstance(prompt[0], (list, tuple, np.ndarray, str))
     return False

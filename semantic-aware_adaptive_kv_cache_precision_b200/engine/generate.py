@@ -164,6 +164,22 @@ def decode_ahead(live: list, first_feed, max_new_tokens: int, stop_ids, launch, 
         settle(in_flight)
 
 
+def stop_ids_of_folder(model_dir, configured=()) -> frozenset:
+    """The end-of-sequence ids generation stops at: `eos_token_id` of the folder's
+    generation_config.json, a number or a list (`src/microinfer/engine.py:1148-1153`; the
+    instruct checkpoints list two there), else the ids that config.json gave
+    (`configured`)."""
+    import json
+    from pathlib import Path
+    if model_dir is not None:
+        path = Path(model_dir) / "generation_config.json"
+        if path.is_file():
+            eos = json.loads(path.read_text()).get("eos_token_id")
+            if eos is not None:
+                return frozenset(int(e) for e in (eos if isinstance(eos, list) else [eos]))
+    return frozenset(int(e) for e in configured)
+
+
 def check_prompt(ids, vocab_size: int, what: str = "token_ids") -> np.ndarray:
     """One sequence of token ids, as the reference checks it
     (`src/microinfer/engine.py:1836-1851`)."""

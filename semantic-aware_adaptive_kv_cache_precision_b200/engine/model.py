@@ -44,6 +44,8 @@ class DecoderModel:
         decls += self.final_norm.tensor_decls()
         if not spec.tie_head:
             decls.append(TensorDecl(spec.head_name, (spec.vocab_size, spec.hidden)))
+        if spec.head_bias_name:
+            decls.append(TensorDecl(spec.head_bias_name, (spec.vocab_size,), init="zeros"))
         return decls
 
     @staticmethod
@@ -52,7 +54,8 @@ class DecoderModel:
         return DecoderModel(spec, "float32", "cpu").tensor_decls()
 
     def load(self, folder) -> None:
-        self._bind(load_checkpoint(folder, self.tensor_decls(), self.mode, self.device))
+        self._bind(load_checkpoint(folder, self.tensor_decls(), self.mode, self.device,
+                                   ignore=self.spec.ignore_tensors))
 
     def load_random(self, seed: int) -> None:
         self._bind(random_arena(self.tensor_decls(), seed, self.spec.init_std, self.mode,
@@ -61,6 +64,7 @@ class DecoderModel:
     def _bind(self, arena) -> None:
         self.embed = arena.view(self.spec.embed_name)
         self.head = self.embed if self.spec.tie_head else arena.view(self.spec.head_name)
+        self.head_bias = arena.view(self.spec.head_bias_name) if self.spec.head_bias_name else None
         for block in self.blocks:
             block.bind(arena)
         self.final_norm.bind(arena)
@@ -82,12 +86,21 @@ class DecoderModel:
 
     # -- the forward pass ---------------------------------------------------------
 
-    def hidden(self, step, cache) -> torch.Tensor:
+    def hidden(self, step, cache, capture: list | None = None) -> torch.Tensor:
         """The residual stream [T, hidden] (fp32) after the last layer call; the
-        cache entries that the calls own are extended by the step's tokens."""
+        cache entries that the calls own are extended by the step's tokens.
+
+        With `capture` (a list), copies of the stream are appended to it: after the
+        embedding and after every layer call but the last, the order in which the
+        reference captures hidden states (`src/microinfer/model.py:355-364, 398-402`);
+        `final_states` gives the entry that closes that list."""
         if self.arena is None:
             raise RuntimeError("no weights on the device; load a checkpoint first")
         x = ops.embed(step.token_ids, self.embed)
+        if self.spec.embed_scale != 1.0:
+            ops.scale_cap_(x, self.spec.embed_scale)
+        if capture is not None:
+            capture.append(x.clone())
         written = set()
         pending = None          # a block's last output, not yet added to the stream
         last = len(self.spec.run_order) - 1
@@ -96,22 +109,32 @@ class DecoderModel:
             block = self.blocks[call.block]
             if getattr(block, "carries_pending", False):
                 pending = block.forward(x, step, view, call.cache not in written, pending,
-                                        leave_pending=i < last)
+                                        leave_pending=i < last and capture is None)
             else:
                 if pending is not None:
                     ops.add_into(x, pending)
                 block.forward(x, step, view, call.cache not in written)
                 pending = None
             written.add(call.cache)
+            if capture is not None and i < last:
+                capture.append(x.clone())
         if pending is not None:
             ops.add_into(x, pending)
         return x
+
+    def final_states(self, x: torch.Tensor) -> torch.Tensor:
+        """The stream after the final norm, fp32 [T, hidden]: the last entry of the captured
+        hidden states."""
+        return self.final_norm.forward(x, out_dtype=torch.float32)
 
     def logits(self, x: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
         """fp32 logits [len(rows), vocab] of the token rows `rows` of `x`: only
         these rows go through the final norm and the output head."""
         normed = self.final_norm.forward(x, rows=rows)
-        return ops.linear(normed, self.head, out_dtype=torch.float32)
+        out = ops.linear(normed, self.head, self.head_bias, out_dtype=torch.float32)
+        if self.spec.logit_scale != 1.0 or self.spec.logit_softcap:
+            ops.scale_cap_(out, self.spec.logit_scale, self.spec.logit_softcap)
+        return out
 
 
 def _strip(name: str) -> str:

@@ -10,7 +10,9 @@ A trace is a stream of JSON objects, one a line:
     {"step": 0, "entries": [{"id": "a", "tokens": [5, 17, 3], "want": [0, 2]}], "end": []}
 
 `entries` gives each request's next tokens and the places among them whose
-logits are wanted; `end` names requests that are finished after the step. For a
+logits are wanted; `end` names requests that are finished after the step. A
+request starts at the step that names it first; requests that start and
+requests that go on (by one token or by many) may share a step. For a
 step that wants something, `<out>/<step>.f32` receives the logits at the wanted
 places in the order of the entries, little-endian fp32 [wanted, vocab]. After
 every step the line `done <step>` is printed and flushed.
@@ -43,11 +45,13 @@ class Replayer:
             raise TraceError("a step needs a 'step' field")
         step = record["step"]
         entries = record.get("entries", [])
-        fresh = [e["id"] for e in entries if e["id"] not in self.slot_of]
+        names = [e["id"] for e in entries]
+        if len(set(names)) != len(names):
+            raise TraceError(f"step {step}: a request appears twice")
+        # requests not seen before start here; they may do so beside requests that go on
+        # (the step function takes both in one batch)
+        fresh = [n for n in names if n not in self.slot_of]
         if fresh:
-            if len(fresh) != len(entries):
-                raise TraceError(f"step {step}: requests {fresh} start while others go on; the "
-                                 "requests of a step either all start or all go on")
             for request, slot in zip(fresh, self.engine.open(len(fresh))):
                 self.slot_of[request] = slot
         wanted = 0

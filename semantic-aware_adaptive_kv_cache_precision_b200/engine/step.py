@@ -18,7 +18,7 @@ from dataclasses import dataclass, field
 import numpy as np
 import torch
 
-QUERY_TILE = 64       # tokens per query tile of the mma.sync prefill kernel; also the cache block
+from ..cache import BLOCK     # positions per cache block: block lists are counted in it
 
 
 @dataclass
@@ -42,7 +42,6 @@ class StepContext:
     max_len: int = 0
     is_decode: bool = False           # every sequence brings exactly one token
     max_len_bound: int = 0            # a bound on max_len that changes rarely (block-list width)
-    q_tiles: torch.Tensor | None = None   # int32 [n, 4]: (sequence, first row, rows <= 64, first position)
     plans: dict = field(default_factory=dict)   # what a part worked out for this step, for its
                                                 # other layers to use again (key chosen by the part)
 
@@ -88,17 +87,10 @@ class StepStager:
         ends = [s + c for s, c in zip(starts, counts)]
         # (rounded up to a multiple of 8 blocks, so that a decode loop keeps one shape for
         # 512 steps and its captured graph can be replayed)
-        width = -(-max(1, -(-max(ends, default=1) // QUERY_TILE)) // 8) * 8
+        width = -(-max(1, -(-max(ends, default=1) // BLOCK)) // 8) * 8
         tables = [np.ascontiguousarray(t[:, :min(width, t.shape[1])]) for t in tables]
-        # query tiles of up to 64 tokens, none crossing a sequence's end
-        tiles, row = [], 0
-        for i, (s, c) in enumerate(zip(starts, counts)):
-            for a in range(0, c, QUERY_TILE):
-                tiles.append((i, row + a, min(QUERY_TILE, c - a), s + a))
-            row += c
-        tiles.sort(key=lambda t: -(t[3] + t[2]))     # the tiles with the most keys start first
         fields = [("token_ids", T), ("positions", T), ("token_seq", T), ("cu_seqlens", B + 1),
-                  ("seq_lens", B), ("slots", B), ("want", W), ("q_tiles", 4 * len(tiles))]
+                  ("seq_lens", B), ("slots", B), ("want", W)]
         fields += [(f"table{g}", t.size) for g, t in enumerate(tables)]
         offsets, total = {}, 0
         for name, n in fields:
@@ -126,7 +118,6 @@ class StepStager:
         put("seq_lens", [s + c for s, c in zip(starts, counts)])
         put("slots", slots)
         put("want", want_rows)
-        put("q_tiles", np.asarray(tiles, dtype=np.int32))
         for g, t in enumerate(tables):
             put(f"table{g}", t)
         self.last_bytes = 4 * total
@@ -147,5 +138,4 @@ class StepStager:
             tables=dev_tables, new_counts=counts, starts=list(starts), host_slots=list(slots),
             max_position=max(ends) - 1 if ends else 0, max_new=max(counts, default=0),
             max_len=max(ends, default=0), is_decode=all(c == 1 for c in counts),
-            max_len_bound=min(width, max((t.shape[1] for t in tables), default=width)) * QUERY_TILE,
-            q_tiles=view("q_tiles", 4 * len(tiles)).view(len(tiles), 4))
+            max_len_bound=min(width, max((t.shape[1] for t in tables), default=width)) * BLOCK)

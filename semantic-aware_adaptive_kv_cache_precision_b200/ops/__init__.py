@@ -15,12 +15,15 @@ from ._lib import (BF16, CACHE_BLOCK, F32, KernelError, call, dtype_code, plain_
 from .linear import Deferred, gated_up, linear
 from . import gemm_tc
 from .attention import (attention_decode, attention_prefill, attention_prefill_tc, decode_splits,
-                        fast_path_takes, kernel_errors, plan_wide_tiles, tc_prefill_takes, upload_wide_plan)
+                        forget_descriptors,
+                        fast_path_takes, kernel_errors, plan_wide_tiles, tc_prefill_takes, upload_query_tiles,
+                        upload_wide_plan)
 
 __all__ = ["CACHE_BLOCK", "KernelError", "embed", "rms_norm", "rope_store", "attention_plain",
            "attention_decode", "attention_prefill", "attention_prefill_tc", "tc_prefill_takes", "plan_wide_tiles", "upload_wide_plan",
-           "decode_splits", "fast_path_takes",
-           "kernel_errors", "gated_silu", "gated_up", "gemm_tc", "add_into", "linear", "choose", "Deferred"]
+           "upload_query_tiles",
+           "decode_splits", "fast_path_takes", "forget_descriptors",
+           "kernel_errors", "gated_silu", "gated_up", "gemm_tc", "add_into", "scale_cap_", "linear", "choose", "Deferred"]
 
 
 def _check(cond: bool, message: str) -> None:
@@ -150,6 +153,15 @@ def add_into(acc: torch.Tensor, y: torch.Tensor) -> None:
     _check(acc.dtype == torch.float32 and acc.is_contiguous() and y.is_contiguous()
            and acc.shape == y.shape, "acc: fp32, same shape as y, both contiguous")
     call("sakv_add_into", ptr(acc), ptr(y), dtype_code(y.dtype), acc.numel())
+
+
+def scale_cap_(x: torch.Tensor, scale: float = 1.0, cap: float | None = None) -> torch.Tensor:
+    """In place on fp32 `x`: `x *= scale`, then with `cap` c, `x = c * tanh(x / c)`."""
+    require_cuda(x)
+    _check(x.dtype == torch.float32 and x.is_contiguous(), "x: contiguous fp32")
+    _check(cap is None or cap > 0, "cap must be positive")
+    call("sakv_scale_cap", ptr(x), x.numel(), float(scale), float(cap or 0.0))
+    return x
 
 
 def choose(logits: torch.Tensor, temperature: float = 0.0, seed: int = 0,

@@ -24,6 +24,7 @@ SIGNATURES = {
     "sakv_embed": ("elementwise", [P, P, I, P, I, I, I, P]),
     "sakv_gated_silu": ("elementwise", [P, P, I, I, I, P]),
     "sakv_add_into": ("elementwise", [P, P, I, L, P]),
+    "sakv_scale_cap": ("elementwise", [P, L, F, F, P]),
     "sakv_rmsnorm": ("norm", [P, P, I, L, P, P, I, P, I, I, I, F, P]),
     "sakv_rope_store": ("rope", [P, I, L, P, P, P, I, P, P, I, P, P, I, I, I, I, I, P]),
     "sakv_attention_plain": ("attention_plain",
@@ -31,7 +32,7 @@ SIGNATURES = {
     "sakv_gemm_f32": ("gemm_f32", [P, L, P, P, P, L, I, I, I, I, P]),
     "sakv_choose": ("sampling", [P, L, I, I, F, U, P, P, P, P, P, P, P]),
     "sakv_decode_attention": ("attention_decode",
-                              [P, P, P, L, P, P, I, P, P, P, I, I, I, I, I, F, I, P, P, P, P, P]),
+                              [P, P, P, L, P, P, I, P, P, P, I, I, I, I, I, F, I, P, P, I, P, P, P]),
     "sakv_prefill_attention": ("attention_prefill",
                                [P, P, P, L, P, P, I, P, P, I, I, I, I, F, I, P]),
     "sakv_prefill_attention_tc": ("attention_prefill_tc",
@@ -103,6 +104,19 @@ def stream() -> int:
     if _raw_stream is not None:
         return _raw_stream(torch.cuda.current_device())
     return torch.cuda.current_stream().cuda_stream
+
+
+_sm_counts: dict = {}
+
+
+def sm_count(device=None) -> int:
+    """Streaming multiprocessors of `device` (default: the current one), asked once."""
+    index = torch.cuda.current_device() if device is None else torch.device(device).index
+    if index is None:
+        index = torch.cuda.current_device()
+    if index not in _sm_counts:
+        _sm_counts[index] = torch.cuda.get_device_properties(index).multi_processor_count
+    return _sm_counts[index]
 
 
 def require_cuda(*tensors) -> None:

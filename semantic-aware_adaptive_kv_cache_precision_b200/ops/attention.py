@@ -8,9 +8,8 @@ import ctypes
 import torch
 
 from . import _lib
-from ._lib import CACHE_BLOCK, KernelError, call, plain_function, ptr, require_cuda
+from ._lib import CACHE_BLOCK, KernelError, call, plain_function, ptr, require_cuda, sm_count
 
-SM_COUNT = 148
 _maps: dict = {}
 
 
@@ -23,7 +22,7 @@ def fast_path_takes(dtype: torch.dtype, heads: int, kv_heads: int, head_dim: int
 def tensor_map(cache: torch.Tensor):
     """The TMA descriptor of one cache entry [blocks, kv_heads, 64, head_dim] (bf16),
     made once per tensor and kept; returns the address of its 128 bytes on the host."""
-    key = (cache.data_ptr(), tuple(cache.shape))
+    key = (cache.data_ptr(), tuple(cache.shape), cache.stride(), cache.dtype)
     hit = _maps.get(key)
     if hit is None:
         if cache.dtype != torch.bfloat16 or not cache.is_contiguous() or cache.dim() != 4 \
@@ -41,17 +40,18 @@ def tensor_map(cache: torch.Tensor):
     return hit[1]
 
 
-def decode_splits(sequences: int, kv_heads: int, max_len: int) -> int:
+def decode_splits(sequences: int, kv_heads: int, max_len: int, sms: int | None = None) -> int:
     """How many ways to split the keys. Either one block per SM, however short its run of
     keys, or, when that leaves runs of many tiles, two blocks per SM with at least three
     tiles each: more tiles in flight. Measured at 2,053 keys, 2 KV heads (us, fold included):
     8 sequences 9 splits 8.1 (12: 8.7); 16 sequences 4: 12.6, 9: 10.5; 32 sequences 2: 22.9,
     4: 16.1; 64 sequences 1: 35.5, 2: 28.3."""
+    sms = sms or sm_count()
     tiles = max(1, -(-max_len // CACHE_BLOCK))
     pairs = max(1, sequences * kv_heads)
-    one_each = max(1, min(tiles, SM_COUNT // pairs))
-    two_each = max(1, min(tiles // 3, 2 * SM_COUNT // pairs))
-    if two_each * pairs > SM_COUNT and 2 * two_each >= 3 * one_each:
+    one_each = max(1, min(tiles, sms // pairs))
+    two_each = max(1, min(tiles // 3, 2 * sms // pairs))
+    if two_each * pairs > sms and 2 * two_each >= 3 * one_each:
         return min(two_each, 64)
     return min(one_each, 64)
 
@@ -96,7 +96,7 @@ def attention_decode(qkv: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Te
 def _rotary_arguments(rotary, write_cache, qkv, k_cache, v_cache, heads, kv_heads, head_dim,
                       max_len):
     if rotary is None:
-        return None, None, None, None
+        return None, None, 0, None, None
     cos, sin = rotary
     if cos.dtype != torch.float32 or sin.dtype != torch.float32 or cos.shape != sin.shape \
             or cos.dim() != 2 or cos.shape[1] * 2 != head_dim or not cos.is_contiguous() \
@@ -107,8 +107,23 @@ def _rotary_arguments(rotary, write_cache, qkv, k_cache, v_cache, heads, kv_head
         raise KernelError("attention_decode: with rotary tables qkv must be the whole "
                           "[q | k | v] projection, rows 16-byte aligned")
     if write_cache:
-        return ptr(cos), ptr(sin), ptr(k_cache), ptr(v_cache)
-    return ptr(cos), ptr(sin), None, None
+        return ptr(cos), ptr(sin), cos.shape[0], ptr(k_cache), ptr(v_cache)
+    return ptr(cos), ptr(sin), cos.shape[0], None, None
+
+
+def upload_query_tiles(starts, counts, device, tile: int = 64) -> torch.Tensor:
+    """The launch plan of `attention_prefill` for sequences that hold `starts[i]` positions
+    and bring `counts[i]` tokens: int32 [n, 4] on the device, one row (sequence, first token
+    row, rows <= 64, first position) per query tile, none crossing a sequence's end, the
+    tiles with the most keys first."""
+    tiles, row = [], 0
+    for i, (s, c) in enumerate(zip(starts, counts)):
+        for a in range(0, c, tile):
+            tiles.append((i, row + a, min(tile, c - a), s + a))
+        row += c
+    tiles.sort(key=lambda t: -(t[3] + t[2]))
+    flat = torch.tensor(tiles, dtype=torch.int32).reshape(-1, 4)
+    return flat.pin_memory().to(device, non_blocking=True)
 
 
 def attention_prefill(qkv: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
@@ -138,7 +153,7 @@ def tc_prefill_takes(dtype: torch.dtype, heads: int, kv_heads: int, head_dim: in
 
 
 def plan_wide_tiles(starts, counts, heads: int, window=None, tile: int = 128,
-                    slots: int = 2 * SM_COUNT):
+                    slots: int | None = None):
     """Work items and folds of the tcgen05 prefill kernel for sequences that hold `starts[i]`
     positions and bring `counts[i]` tokens. Each query tile of up to 128 tokens walks the key
     tiles (64 keys) its rows can see. When all blocks of the step run at once (`slots` of
@@ -146,6 +161,8 @@ def plan_wide_tiles(starts, counts, heads: int, window=None, tile: int = 128,
     are dealt to several blocks that leave partials to be folded; with more blocks than that
     the fold costs more than the balance gains (measured: 2,048 tokens 46 -> 38 us, 4,096
     tokens 92 -> 98 us). Returns (work [n, 8], folds [m, 4], partials)."""
+    if slots is None:
+        slots = 2 * sm_count()                   # two blocks of the kernel fit an SM
     tiles, row = [], 0
     for i, (s, c) in enumerate(zip(starts, counts)):
         for a in range(0, c, tile):
@@ -230,6 +247,19 @@ def attention_prefill_tc(qkv: torch.Tensor, k_cache: torch.Tensor, v_cache: torc
     if n_folds:
         _lib.launches += 1          # the call launched the fold kernel too
     return out
+
+
+def forget_descriptors(*tensors) -> None:
+    """Drop the kept TMA descriptors (of the cache and of weight matrices) that point into
+    the memory of `tensors`. Whoever frees device memory that kernels of this library have
+    read calls this, so that a later tensor at the same address gets a descriptor of its own
+    and the tables do not grow with every model a process has loaded."""
+    from . import gemm_tc, gemm_wide
+    spans = [(t.data_ptr(), t.data_ptr() + t.numel() * t.element_size())
+             for t in tensors if t is not None and t.numel()]
+    for table in (_maps, gemm_tc._weight_maps, gemm_wide._weight_maps):
+        for key in [k for k in table if any(lo <= k[0] < hi for lo, hi in spans)]:
+            del table[key]
 
 
 def kernel_errors() -> dict:

@@ -7,9 +7,8 @@ import ctypes
 
 import torch
 
-from ._lib import BF16, F32, KernelError, call, dtype_code, plain_function, ptr
+from ._lib import BF16, F32, KernelError, call, dtype_code, plain_function, ptr, sm_count
 
-SM_COUNT = 148
 EPI_BF16, EPI_F32, EPI_ACCUM, EPI_GATED = 0, 1, 2, 3
 
 _weight_maps: dict = {}
@@ -38,7 +37,7 @@ def _make_map(t: torch.Tensor, box_rows: int):
 
 
 def _weight_map(weight: torch.Tensor) -> int:
-    key = (weight.data_ptr(), tuple(weight.shape))
+    key = (weight.data_ptr(), tuple(weight.shape), weight.stride(), weight.dtype)
     hit = _weight_maps.get(key)
     if hit is None:
         hit = _make_map(weight, 128)
@@ -62,8 +61,8 @@ def _blocks_at_once(mt: int, dual: bool, splits: int) -> int:
     key = (mt, dual, splits)
     if key not in _cluster_room:
         clusters = plain_function("sakv_gemm_tc_max_clusters")(mt, int(dual), splits)
-        _cluster_room[key] = min(SM_COUNT, clusters * splits) if clusters > 0 else \
-            (SM_COUNT // splits) * splits * 3 // 4
+        _cluster_room[key] = min(sm_count(), clusters * splits) if clusters > 0 else \
+            (sm_count() // splits) * splits * 3 // 4
     return _cluster_room[key]
 
 
@@ -71,7 +70,7 @@ def choose_splits(n_tiles: int, m_tiles: int, k: int, mt: int = 16, dual: bool =
     """Split K over a cluster so that as many SMs as possible pull weights in ONE wave
     (fewer splits on a tie); no split when the tiles alone fill most of the GPU."""
     tiles = n_tiles * m_tiles
-    if tiles * 4 >= SM_COUNT * 3:
+    if tiles * 4 >= sm_count() * 3:
         return 1
     best, best_blocks = 1, tiles
     for splits in range(2, MAX_SPLITS + 1):
@@ -93,7 +92,7 @@ def choose_parts(m: int, n: int, k: int) -> tuple:
     mt = token_tile(m, False)
     tiles = -(-n // 128) * -(-m // mt)
     steps = -(-k // 64)
-    if tiles * 8 * 2 > SM_COUNT * 3 // 2 or steps < 64:
+    if tiles * 8 * 2 > sm_count() * 3 // 2 or steps < 64:
         return 1, 0
     per = -(-steps // 16)
     if -(-steps // per) != 16:

@@ -37,7 +37,7 @@ def _make_map(t: torch.Tensor):
 
 
 def _weight_map(weight: torch.Tensor) -> int:
-    key = (weight.data_ptr(), tuple(weight.shape))
+    key = (weight.data_ptr(), tuple(weight.shape), weight.stride(), weight.dtype)
     hit = _weight_maps.get(key)
     if hit is None:
         hit = _weight_maps[key] = _make_map(weight)

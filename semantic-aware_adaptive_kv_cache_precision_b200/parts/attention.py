@@ -115,7 +115,11 @@ class GQAAttention(Part):
                 return ops.attention_prefill_tc(qkv, view.keys, view.values, *plan,
                                                 step.seq_lens, view.block_table, s.heads,
                                                 s.kv_heads, s.head_dim, s.scale, s.window)
-            return ops.attention_prefill(qkv, view.keys, view.values, step.q_tiles,
+            tiles = step.plans.get("query_tiles_64")
+            if tiles is None:          # the same for every attention layer: made once a step
+                tiles = step.plans["query_tiles_64"] = ops.upload_query_tiles(
+                    step.starts, step.new_counts, qkv.device)
+            return ops.attention_prefill(qkv, view.keys, view.values, tiles,
                                          step.seq_lens, view.block_table, s.heads, s.kv_heads,
                                          s.head_dim, s.scale, s.window)
         return ops.attention_plain(qkv, view.keys, view.values, step.positions, step.token_seq,

@@ -20,6 +20,15 @@ Block           forward(x_fp32 [T, H], step, view, write_cache); updates x in pl
 `step` is the `engine.step.StepContext` of the running step: the step's tokens,
 positions, sequences and block tables on the device. `view` is the
 `cache.EntryView` of the cache entry that this layer call reads or writes.
+
+Steps whose shape repeats are captured in CUDA graphs and replayed. A replay
+repeats the launches of the capture, Python numbers included; only what lies on
+the device is fresh (`token_ids`, `positions`, `token_seq`, `seq_lens`, `slots`,
+`want`, the block tables). Of the host-side facts, a graph is keyed by
+`new_counts` and, for a model with per-sequence state, by `host_slots`; a
+prefill graph also by `starts`. A part whose launches depend on anything else on
+the host (`starts`, `max_position` or `max_len` in a decode step, or a value read
+back from the device) sets `graph_safe = False`.
 """
 
 from __future__ import annotations

@@ -21,6 +21,7 @@ from pathlib import Path
 
 import torch
 
+from ..errors import allocate
 from .decl import TensorDecl
 from .safetensors_io import STORED, SafetensorsFile, WeightError
 
@@ -72,12 +73,17 @@ class Checkpoint:
         return list(self.where)
 
 
-def check_tensors(checkpoint: Checkpoint, decls: list[TensorDecl], source: str) -> None:
+def check_tensors(checkpoint: Checkpoint, decls: list[TensorDecl], source: str,
+                  ignore=()) -> None:
     """Raise one WeightError that lists every missing tensor, every unexpected
     tensor and every wrong shape or kind; silent if the checkpoint holds exactly
-    what `decls` say."""
+    what `decls` say. Names that match one of the shell-style patterns in `ignore`
+    (an architecture's buffers that some exporters write and no part reads) are
+    not counted as unexpected."""
+    from fnmatch import fnmatchcase
     expected = {d.name: d for d in decls}
-    found = set(checkpoint.names())
+    found = {n for n in checkpoint.names()
+             if n in expected or not any(fnmatchcase(n, pattern) for pattern in ignore)}
     missing = [f"    {n}: missing (shape {tuple(expected[n].shape)})"
                for n in expected if n not in found]
     unexpected = [f"    {n}: unexpected, not implied by {source} "
@@ -125,7 +131,9 @@ class WeightArena:
             end = start + nbytes
             previous = d
         self.nbytes = -(-end // ALIGNMENT) * ALIGNMENT
-        raw = torch.empty(self.nbytes + ALIGNMENT, dtype=torch.uint8, device=device)
+        raw = allocate(lambda: torch.empty(self.nbytes + ALIGNMENT, dtype=torch.uint8,
+                                           device=device),
+                       "the model's weights", self.nbytes + ALIGNMENT)
         shift = -raw.data_ptr() % ALIGNMENT          # device allocations are aligned already
         self.buffer = raw[shift:shift + max(self.nbytes, 1)]
 
@@ -156,12 +164,13 @@ def _numel(shape) -> int:
     return n
 
 
-def load_checkpoint(folder, decls: list[TensorDecl], mode: str, device, source: str = "config.json"):
+def load_checkpoint(folder, decls: list[TensorDecl], mode: str, device,
+                    source: str = "config.json", ignore=()):
     """Check, allocate, copy. Returns the arena; nothing is allocated unless the
     whole checkpoint fits the declarations, and a NaN or infinity in any tensor
     is refused by name (`src/microinfer/weights.py:153-174`)."""
     checkpoint = Checkpoint(folder)
-    check_tensors(checkpoint, decls, source)
+    check_tensors(checkpoint, decls, source, ignore)
     dtypes = {d.name: device_dtype(checkpoint.info(d.name).dtype, mode) for d in decls}
     arena = WeightArena(decls, dtypes, device)
     bad = []

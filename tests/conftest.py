@@ -96,6 +96,27 @@ def model_folders(tmp_path_factory):
     return get
 
 
+@pytest.fixture(scope="session")
+def varied_folders(tmp_path_factory):
+    """The tiny configurations with weights drawn five times as wide (`initializer_range`
+    0.1): with the usual 0.02 a tied model repeats one token for ever, which makes "the
+    engine generates the plain model's tokens" say little; these generate varied tokens."""
+    from semantic_aware_adaptive_kv_cache_precision_b200 import write_random_model
+    root = tmp_path_factory.mktemp("varied")
+    made = {}
+
+    def get(name: str, dtype: str = "float32") -> Path:
+        key = (name, dtype)
+        if key not in made:
+            config, seed = TINY[name]
+            made[key] = write_random_model(root / f"varied_{name}_{dtype}",
+                                           dict(config, initializer_range=0.1), seed,
+                                           dtype=dtype)
+        return made[key]
+
+    return get
+
+
 def prompts_for(name: str, lengths, seed: int = 0):
     config, _ = TINY[name]
     rng = np.random.default_rng(seed + 100)

@@ -217,6 +217,31 @@ def hidden_states(config: dict, tensors: dict, ids) -> list[np.ndarray]:
     return states
 
 
+def cache_contents(config: dict, tensors: dict, ids) -> tuple[np.ndarray, np.ndarray]:
+    """What a cache holds after the whole sequence: per layer the rotated keys (with their
+    bias, `tools/conditioning.py:70-71`) and the values, each (layers, n, kv_heads,
+    head_dim). The reference reads its own cache back the same way
+    (`src/microinfer/engine.py:1819-1834`; there the keys are stored without the bias)."""
+    ids = np.asarray(ids)
+    n = len(ids)
+    positions = np.arange(n)
+    kv_heads = config["num_key_value_heads"]
+    head_dim = config.get("head_dim") or config["hidden_size"] // config["num_attention_heads"]
+    cos, sin = rope_angles(positions, head_dim, config["rope_theta"])
+    x = embed(tensors["model.embed_tokens.weight"], ids)
+    keys, values = [], []
+    for layer in range(config["num_hidden_layers"]):
+        a = f"model.layers.{layer}.self_attn."
+        h = rms_norm(x, tensors[f"model.layers.{layer}.input_layernorm.weight"],
+                     config["rms_norm_eps"])
+        k = linear(h, tensors[a + "k_proj.weight"], tensors[a + "k_proj.bias"])
+        v = linear(h, tensors[a + "v_proj.weight"], tensors[a + "v_proj.bias"])
+        keys.append(rotate_half(k.reshape(n, kv_heads, head_dim), cos, sin))
+        values.append(v.reshape(n, kv_heads, head_dim))
+        x = decoder_layer(x, tensors, config, layer, positions)
+    return np.stack(keys), np.stack(values)
+
+
 def lm_head(normed, config: dict, tensors: dict) -> np.ndarray:
     """`logits = y head^T`, the head being the embedding when
     `tie_word_embeddings` (`src/microinfer/model.py:76, 405-413`)."""
@@ -225,10 +250,12 @@ def lm_head(normed, config: dict, tensors: dict) -> np.ndarray:
     return normed @ head.T
 
 
-def forward(config: dict, tensors: dict, ids) -> np.ndarray:
+def forward(config: dict, tensors: dict, ids, rows=None) -> np.ndarray:
     """Logits `(len(ids), vocab)` of one whole sequence
-    (`src/microinfer/engine.py:1157-1178`)."""
-    return lm_head(hidden_states(config, tensors, ids)[-1], config, tensors)
+    (`src/microinfer/engine.py:1157-1178`); with `rows`, of those positions only
+    (a large vocabulary makes the head the longest part of this slow model)."""
+    normed = hidden_states(config, tensors, ids)[-1]
+    return lm_head(normed if rows is None else normed[np.asarray(rows)], config, tensors)
 
 
 # --------------------------------------------------------------------------

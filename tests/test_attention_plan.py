@@ -56,7 +56,7 @@ def test_every_key_tile_once(starts, counts, heads, window, slots):
 def test_many_blocks_are_left_whole():
     """A step with more blocks than run at once is not cut: the fold would cost more than
     the balance gains."""
-    work, folds, partials = plan_wide_tiles([0], [4096], 12, None)
+    work, folds, partials = plan_wide_tiles([0], [4096], 12, None, slots=296)
     assert not folds and partials == 0
-    work, folds, partials = plan_wide_tiles([0], [2048], 12, None)
+    work, folds, partials = plan_wide_tiles([0], [2048], 12, None, slots=296)
     assert folds and max(w[5] for w in work) <= 16

@@ -139,3 +139,47 @@ def test_poisoned_blocks():
     cache.close([a])
     assert torch.isnan(cache.groups[0].keys[0, block]).all()
     assert not torch.isnan(cache.groups[0].keys[0, 1 - block]).any()
+
+
+def test_keys_and_values_of_their_own_widths_and_type():
+    """A need may give values another width than keys, no values at all, or a type of its
+    own; entries with different needs get storage of their own."""
+    needs = [KVNeed(2, 16), KVNeed(2, 16, value_dim=40), KVNeed(1, 24, value_dim=0),
+             KVNeed(2, 16, dtype="float32"), KVNeed(2, 16, value_dim=40)]
+    cache = SequenceCache(needs, 4 * BLOCK, 256, torch.bfloat16, "cpu", poison_freed=True)
+    assert len(cache.groups) == 4
+    by_need = {g.need: g for g in cache.groups}
+    wide = by_need[KVNeed(2, 16, value_dim=40)]
+    assert wide.keys.shape == (2, 4, 2, BLOCK, 16) and wide.values.shape == (2, 4, 2, BLOCK, 40)
+    latent = by_need[KVNeed(1, 24, value_dim=0)]
+    assert latent.values is None and latent.keys.shape == (1, 4, 1, BLOCK, 24)
+    assert by_need[KVNeed(2, 16, dtype="float32")].keys.dtype == torch.float32
+    assert by_need[KVNeed(2, 16)].keys.dtype == torch.bfloat16
+    expected = sum(t.numel() * t.element_size() for g in cache.groups
+                   for t in (g.keys, g.values) if t is not None)
+    assert cache.nbytes == expected
+    (a,) = cache.open(1)
+    cache.reserve([a], [70])
+    view = cache.entry_view(2, [torch.zeros(1, 2, dtype=torch.int32)] * 4)
+    assert view.values is None and view.keys.shape == (4, 1, BLOCK, 24)
+    view = cache.entry_view(4, [torch.zeros(1, 2, dtype=torch.int32)] * 4)
+    assert view.values.shape == (4, 2, BLOCK, 40)
+    cache.close([a])          # freed blocks are poisoned, the missing values are no obstacle
+    cache.check()
+    with pytest.raises(TypeError, match="dtype"):
+        SequenceCache([KVNeed(1, 16, dtype="float16")], BLOCK, 64, torch.float32, "cpu")
+
+
+def test_a_cache_the_device_cannot_hold_is_a_typed_error(monkeypatch):
+    from semantic_aware_adaptive_kv_cache_precision_b200 import OutOfDeviceMemory
+    real, calls = torch.zeros, []
+
+    def no_room(*args, **kwargs):
+        calls.append(args)
+        if len(calls) == 3:           # the second group's keys: the first group is built
+            raise torch.OutOfMemoryError("injected")
+        return real(*args, **kwargs)
+
+    monkeypatch.setattr(torch, "zeros", no_room)
+    with pytest.raises(OutOfDeviceMemory, match="a cache of 4 blocks"):
+        SequenceCache([KVNeed(2, 16), KVNeed(1, 32)], 4 * BLOCK, 256, torch.float32, "cpu")

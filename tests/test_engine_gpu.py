@@ -187,9 +187,10 @@ def test_greedy_generation_through_the_entry_point(engines, model_folders):
             got = engine.generate([p.tolist() for p in prompts], 8, stop_token_ids=[stop])
             for g, w, e in zip(got, want, engine.endings):
                 cut = w.index(stop) + 1 if stop in w else len(w)
-                assert g.tolist() == w[:cut] and e.positions == len(g) + e.positions - len(g)
+                assert g.tolist() == w[:cut]
                 assert e.reason == ("stop" if stop in w else "length")
-            assert engine.endings[who].positions == len(prompts[who]) + len(got[who]) - 1
+            for p, g, e in zip(prompts, got, engine.endings):
+                assert e.positions == len(p) + len(g) - 1      # the last token is never fed
     assert engine.cache.slots.held == 0
 
 
@@ -370,3 +371,209 @@ def test_many_requests_in_batches_end_as_they_do_alone(model_folders):
     assert [e.positions for e in engine.endings] == [len(p) + len(w) - 1 for p, w in zip(prompts, want)]
     assert engine.cache.slots.held == 0
     engine.cache.check()
+
+
+# ---- steps whose sequences are at different places --------------------------------------------
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["B", "D"])
+def test_a_step_may_mix_starting_continuing_and_decoding_sequences(name, dtype, engines):
+    """One step in which sequence a starts with 70 tokens, b goes on with 5 after 64 and c
+    with 1 after 200; then a step in which a decodes, b brings 3 more and d starts. Every
+    position's logits are those of its sequence run alone and whole: to the bit in 32-bit,
+    within rounding in bfloat16."""
+    engine = engines(name, dtype)
+    a, b, c, d = prompts_for(name, [71, 72, 201, 9], seed=70)
+    whole = {k: engine.forward(p) for k, p in zip("abcd", (a, b, c, d))}
+    sa, sb, sc = engine.open(3)
+    engine.step([sb, sc], [b[:64], c[:200]], [[], []])
+    out = engine.step([sa, sb, sc], [a[:70], b[64:69], c[200:201]],
+                      [list(range(70)), list(range(5)), [0]]).cpu().numpy()
+    assert_same_logits(out[:70], whole["a"][:70], dtype, "a starts beside others")
+    assert_same_logits(out[70:75], whole["b"][64:69], dtype, "b goes on by five")
+    assert_same_logits(out[75:76], whole["c"][200:201], dtype, "c decodes one")
+    engine.close([sc])
+    (sd,) = engine.open(1)                      # takes the slot c gave back
+    out = engine.step([sd, sa, sb], [d, a[70:71], b[69:72]],
+                      [list(range(9)), [0], [0, 1, 2]]).cpu().numpy()
+    assert_same_logits(out[:9], whole["d"], dtype, "d starts in a freed slot")
+    assert_same_logits(out[9:10], whole["a"][70:71], dtype, "a decodes one")
+    assert_same_logits(out[10:13], whole["b"][69:72], dtype, "b goes on by three")
+    engine.close([sa, sb, sd])
+    engine.cache.check()
+    assert engine.cache.slots.held == 0
+
+
+# ---- generation in bfloat16 on the fast kernels ---------------------------------------------------
+
+@pytest.mark.parametrize("name", ["C", "D"])
+def test_bfloat16_generation_chooses_the_argmax_of_a_forward_pass(name, varied_folders):
+    """`generate` in bfloat16 on head sizes that the tensor-core attention kernels take, that
+    is, through the decode loop that runs ahead of the host, the replayed graphs and the
+    decode attention that rotates and stores on its own way: every token it chose is the
+    argmax of ONE forward pass over the prompt and the tokens (the reference's test of its
+    decode path, `tests/test_inference.py:140-149`), or loses to it by less than the bf16
+    bound (a near tie). The weights are wide enough for the tokens to vary."""
+    from helpers import BF16_RTOL
+    engine = engine_for(varied_folders(name, "bfloat16"), "bfloat16")
+    prompts = prompts_for(name, [5, 70, 131, 40, 64], seed=60)
+    got = engine.generate([p.tolist() for p in prompts], 40, stop_at_eos=False)
+    assert engine.graph_failure is None and len(engine._graphs) >= 1
+    flips = 0
+    for p, g in zip(prompts, got):
+        assert len(g) == 40 and len(set(g.tolist())) > 8, f"tokens do not vary: {g.tolist()}"
+        logits = engine.forward(np.concatenate([p, g[:-1]]))[len(p) - 1:]
+        for k, token in enumerate(g.tolist()):
+            best = int(logits[k].argmax())
+            if token != best:
+                flips += 1
+                assert logits[k, best] - logits[k, token] <= BF16_RTOL * logits[k].std(), \
+                    f"token {k} of a {len(p)}-token prompt: {token} chosen, {best} is the argmax"
+    assert flips <= 20, f"{flips} of 200 tokens lost to a near tie: too many to be chance"
+    assert engine.cache.slots.held == 0
+
+
+def test_greedy_generation_of_varied_tokens(varied_folders):
+    """fp32, tokens that vary (tiny-B with wide weights), through the whole loop: the plain
+    model's tokens exactly, also with a stop token somewhere in the middle of each request."""
+    folder = varied_folders("B", "float32")
+    engine = engine_for(folder, "float32")
+    config, tensors = plain.read_model_folder(folder)
+    prompts = prompts_for("B", [1, 7, 30, 64], seed=61)
+    want = [plain.generate(config, tensors, p, 12) for p in prompts]
+    assert all(len(set(w)) > 4 for w in want)
+    got = engine.generate([p.tolist() for p in prompts], 12, stop_at_eos=False)
+    assert [g.tolist() for g in got] == want
+    for place in (0, 3, 7, 11):
+        stop = want[1][place]
+        got = engine.generate([p.tolist() for p in prompts], 12, stop_token_ids=[stop])
+        for g, w, e in zip(got, want, engine.endings):
+            cut = w.index(stop) + 1 if stop in w else len(w)
+            assert g.tolist() == w[:cut] and e.reason == ("stop" if stop in w else "length")
+        assert len(got[1]) == want[1].index(stop) + 1 <= place + 1
+
+
+def test_generation_stops_at_the_folders_end_of_sequence_ids(varied_folders, tmp_path):
+    """With the default `stop_at_eos=True` the stop ids are those of generation_config.json
+    (a number or a list) if the folder has one, else config.json's `eos_token_id`."""
+    import json
+    import shutil
+    src = varied_folders("B", "float32")
+    config, tensors = plain.read_model_folder(src)
+    prompt = prompts_for("B", [7], seed=61)[0]
+    free = plain.generate(config, tensors, prompt, 12)
+    for eos in (free[4], [free[6], free[2]]):
+        folder = tmp_path / f"eos_{eos if isinstance(eos, int) else 'list'}"
+        shutil.copytree(src, folder)
+        (folder / "generation_config.json").write_text(json.dumps({"eos_token_id": eos}))
+        engine = engine_for(folder, "float32")
+        stops = {eos} if isinstance(eos, int) else set(eos)
+        assert engine.eos_token_ids == frozenset(stops)
+        out = engine.generate(prompt, 12).tolist()
+        cut = min(free.index(s) for s in stops) + 1
+        assert out == free[:cut] and engine.ending.reason == "stop"
+        assert engine.generate(prompt, 12, stop_at_eos=False).tolist() == free
+    # without the file: config.json's ids (tiny-B: 11 and 13)
+    assert engine_for(src, "float32").eos_token_ids == frozenset({11, 13})
+
+
+# ---- the diagnostics: hidden states, the cache read back, the footprint -----------------------------
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_hidden_states_match_the_reference_models(name, engines, model_folders):
+    """`forward(ids, capture_hidden_states=True)`: the embedding's output, the stream after
+    each layer but the last, the last after the final norm, compared layer by layer with the
+    plain model and, for the layers it stored, with what the reference's own float64 model
+    computed (`tests/golden/`)."""
+    from pathlib import Path
+    gold = np.load(Path(__file__).parent / "golden" / f"tiny_{name}.npz")
+    engine = engines(name, "float32")
+    config, tensors = plain.read_model_folder(model_folders(name, "float32"))
+    ids = gold["ids"]
+    logits, states = engine.forward(ids, capture_hidden_states=True)
+    want = plain.hidden_states(config, tensors, ids)
+    assert states.shape == (config["num_hidden_layers"] + 1, len(ids), config["hidden_size"])
+    for i, w in enumerate(want):
+        assert np.abs(states[i] - w).max() <= FP32_RTOL_STATES * np.abs(w).max(), f"state {i}"
+    keep = gold["positions"]
+    np.testing.assert_allclose(states[1][keep], gold["mid_hidden"], rtol=0,
+                               atol=FP32_RTOL_STATES * np.abs(gold["mid_hidden"]).max())
+    np.testing.assert_allclose(states[-1][keep], gold["final_hidden"], rtol=0,
+                               atol=FP32_RTOL_STATES * np.abs(gold["final_hidden"]).max())
+    np.testing.assert_array_equal(logits, engine.forward(ids))     # capturing changes nothing
+
+
+FP32_RTOL_STATES = 2e-5      # as for logits: of the largest magnitude of the compared state
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["B", "D", "W"])
+def test_the_cache_holds_the_plain_models_keys_and_values(name, dtype, engines, model_folders):
+    """`cached_kv` reads the blocks of a prefilled sequence back: rotated keys and values of
+    every layer and position against the plain model's. A wrong block in ONE layer shows
+    here by its layer and position, not only at the logits."""
+    engine = engines(name, dtype)
+    config, tensors = plain.read_model_folder(model_folders(name, stored(dtype)))
+    ids = prompts_for(name, [150], seed=80)[0]
+    keys, values = engine.cached_kv(ids)
+    want_k, want_v = plain.cache_contents(config, tensors, ids)
+    assert keys.shape == want_k.shape and values.shape == want_v.shape
+    tol = 2e-5 if dtype == "float32" else 2e-2
+    for layer in range(config["num_hidden_layers"]):
+        window = plain.layer_window(config, layer)
+        first = 0 if window is None else (max(0, len(ids) - window + 1) // 64) * 64
+        assert np.isnan(keys[layer, :first]).all()           # blocks the window gave back
+        for got, want, what in ((keys, want_k, "keys"), (values, want_v, "values")):
+            diff = np.abs(got[layer, first:] - want[layer, first:])
+            assert diff.max() <= tol * np.abs(want[layer]).max(), \
+                f"{what} of layer {layer}: position {np.unravel_index(diff.argmax(), diff.shape)[0] + first}"
+    assert engine.cache.slots.held == 0
+
+
+def test_footprint_counts_weights_and_cache(model_folders):
+    engine = engine_for(model_folders("B", "bfloat16"), "bfloat16", max_tokens=640)
+    before = engine.footprint()
+    assert before["kv_cache"] == 0 and before["weights"] == engine.model.arena.nbytes > 0
+    engine.forward([1, 2, 3])
+    after = engine.footprint()
+    # three layers of one KV head of 32: keys and values, 10 blocks of 64, two bytes each
+    assert after["kv_cache"] == 3 * 2 * 10 * 64 * 32 * 2
+    assert 0 < after["device_free"] <= after["device_total"]
+
+
+def test_allocation_failures_leave_the_engine_as_it_was(model_folders, monkeypatch):
+    """An allocation that fails while the weights or the cache are built raises the typed
+    error and leaves no half-built state (`tests/test_emergency_downgrade.py:40-54` of the
+    reference injects its failures on the host in the same way)."""
+    from semantic_aware_adaptive_kv_cache_precision_b200 import Engine, OutOfDeviceMemory
+    folder = model_folders("A", "float32")
+    engine = Engine(folder, dtype="float32", max_tokens=256)
+    real_empty, real_zeros = torch.empty, torch.zeros
+    state = {"fail": True}
+
+    def empty(*args, **kwargs):
+        if state["fail"] and kwargs.get("dtype") == torch.uint8:
+            raise torch.OutOfMemoryError("injected")
+        return real_empty(*args, **kwargs)
+
+    def zeros(*args, **kwargs):
+        if state["fail"] and args and isinstance(args[0], tuple) and len(args[0]) == 5:
+            raise torch.OutOfMemoryError("injected")
+        return real_zeros(*args, **kwargs)
+
+    monkeypatch.setattr(torch, "empty", empty)
+    monkeypatch.setattr(torch, "zeros", zeros)
+    with pytest.raises(OutOfDeviceMemory, match="weights"):
+        engine.load_weights()
+    assert not engine._loaded and engine.model.arena is None
+    with pytest.raises(RuntimeError, match="load_weights"):
+        engine.forward([1, 2])
+    state["fail"] = False
+    engine.load_weights()
+    state["fail"] = True
+    with pytest.raises(OutOfDeviceMemory, match="cache"):
+        engine.forward([1, 2])
+    assert engine.cache is None
+    state["fail"] = False
+    ids = prompts_for("A", [9], seed=81)[0]
+    assert_close_to_plain(engine.forward(ids), plain_logits(folder, ids), "float32", "after")

@@ -154,3 +154,16 @@ def test_a_full_cache_ends_what_is_left_after_reading_what_was_in_flight():
     assert [len(r.out) for r in requests] == [3, 3, 3]
     assert [i for i, _ in log["exhausted"]] == [0, 1, 2]
     assert all("no block" in why for _, why in log["exhausted"])
+
+
+def test_stop_ids_come_from_generation_config_if_there_is_one(tmp_path):
+    import json
+    from semantic_aware_adaptive_kv_cache_precision_b200.engine.generate import stop_ids_of_folder
+    assert stop_ids_of_folder(None, (7,)) == frozenset({7})
+    assert stop_ids_of_folder(tmp_path, (7, 8)) == frozenset({7, 8})     # no such file
+    (tmp_path / "generation_config.json").write_text(json.dumps({"eos_token_id": 5}))
+    assert stop_ids_of_folder(tmp_path, (7,)) == frozenset({5})
+    (tmp_path / "generation_config.json").write_text(json.dumps({"eos_token_id": [5, 9]}))
+    assert stop_ids_of_folder(tmp_path, (7,)) == frozenset({5, 9})
+    (tmp_path / "generation_config.json").write_text(json.dumps({"temperature": 0.7}))
+    assert stop_ids_of_folder(tmp_path, (7,)) == frozenset({7})

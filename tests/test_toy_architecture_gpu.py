@@ -182,9 +182,16 @@ def test_toy_architecture_registers_builds_and_steps(dtype, tmp_path):
     rows = [engine.step([slot], [prompts[1][i:i + 1]]).cpu().numpy() for i in range(9)]
     engine.close([slot])
     assert np.abs(np.concatenate(rows) - whole[1]).max() <= tol * np.abs(whole[1]).max()
-    # an unequal batch, twice in a row, so that slots (and their state) are used again
-    for _ in range(2):
-        slots = engine.open(3)
+    # an unequal batch, three times in a row, so that slots (and their state) are used again:
+    # the same slots, then other slots for a batch of the same shape (a captured step that
+    # kept the first batch's slot numbers would update the wrong sequences' state), then the
+    # first ones in another order
+    for round_ in range(3):
+        if round_ == 1:
+            spare, *slots = engine.open(4)
+            engine.close([spare])
+        else:
+            slots = engine.open(3)[::-1] if round_ == 2 else engine.open(3)
         heads = [len(p) - 4 for p in prompts]
         out = engine.step(slots, [p[:h] for p, h in zip(prompts, heads)],
                           [list(range(h)) for h in heads]).cpu().numpy()
@@ -197,7 +204,7 @@ def test_toy_architecture_registers_builds_and_steps(dtype, tmp_path):
         for i in range(3):
             got = np.concatenate(rows[i])
             scale = np.abs(want[i]).max() if dtype == "float32" else want[i].std()
-            assert np.abs(got - want[i]).max() <= tol * scale, f"request {i}"
+            assert np.abs(got - want[i]).max() <= tol * scale, f"round {round_} request {i}"
     engine.cache.check()
     out = engine.generate([p.tolist() for p in prompts[:2]], 5, stop_at_eos=False)
     assert [len(o) for o in out] == [5, 5]

@@ -117,12 +117,34 @@ def test_replay_three_ways(name, dtype, model_folders, tmp_path):
     trace.finish()
 
 
-def test_trace_run_refuses_a_request_joining_a_running_batch(model_folders, tmp_path):
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["B", "D"])
+def test_requests_may_join_a_running_batch(name, dtype, model_folders, tmp_path):
+    """A step may hold requests that start beside requests that go on by one token or by
+    several: a starts with 70 tokens while b brings 5 after 64 and c one after 200. Every
+    position's logits are those of the request replayed alone and whole."""
+    folder = model_folders(name, "float32" if dtype == "float32" else "bfloat16")
+    a, b, c = prompts_for(name, [71, 69, 201], seed=21)
+    trace = Trace(folder, dtype, tmp_path / "out", 512)
+    whole = {}
+    for key, p in (("a", a), ("b", b), ("c", c)):
+        whole[key] = trace.send([entry("w" + key, p, range(len(p)))], end=["w" + key])
+    assert trace.send([entry("b", b[:64], []), entry("c", c[:200], [])]) is None
+    got = trace.send([entry("a", a[:70], range(70)), entry("b", b[64:], range(5)),
+                      entry("c", c[200:], [0])], end=["b", "c"])
+    assert_same_logits(got[:70], whole["a"][:70], dtype, "a starts beside others")
+    assert_same_logits(got[70:75], whole["b"][64:], dtype, "b goes on by five")
+    assert_same_logits(got[75:], whole["c"][200:], dtype, "c goes on by one")
+    got = trace.send([entry("a", a[70:], [0])], end=["a"])
+    assert_same_logits(got, whole["a"][70:], dtype, "a decodes after the mixed step")
+    trace.finish()
+
+
+def test_trace_run_ends_with_an_error_on_a_bad_step(model_folders, tmp_path):
     folder = model_folders("A", "float32")
     trace = Trace(folder, "float32", tmp_path / "out", 256)
     trace.send([entry("a", [1, 2, 3], [2])])
-    trace.proc.stdin.write(json.dumps({"step": 1, "entries": [entry("a", [4], [0]),
-                                                              entry("b", [5, 6], [1])],
-                                       "end": []}) + "\n")
+    trace.proc.stdin.write(json.dumps({"step": 1, "entries": [entry("a", [4], [0])],
+                                       "end": ["nobody"]}) + "\n")
     trace.proc.stdin.close()
     assert trace.proc.wait(timeout=60) != 0

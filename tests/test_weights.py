@@ -145,3 +145,73 @@ def test_random_model_is_a_function_of_seed_and_name(tmp_path):
     assert abs(w.mean()) < 0.002 and abs(w.std() - 0.02) < 0.002
     assert abs(tensors["model.layers.0.self_attn.k_proj.bias"].std() - 0.02) < 0.01
     check_tensors(Checkpoint(a), _decls(TINY_A), "config.json")
+
+
+def test_a_checkpoint_in_two_shards_loads_like_one_file(tmp_path):
+    """`model.safetensors.index.json` names the shard of every tensor; the loader finds
+    each tensor in its shard and the arena is the one a single file gives."""
+    whole = write_random_model(tmp_path / "whole", dict(TINY_B), 1, dtype="bfloat16")
+    f = SafetensorsFile(whole / "model.safetensors")
+    names = list(f.infos)
+    halves = {"model-00001-of-00002.safetensors": names[:len(names) // 2],
+              "model-00002-of-00002.safetensors": names[len(names) // 2:]}
+    sharded = tmp_path / "sharded"
+    sharded.mkdir()
+    (sharded / "config.json").write_text((whole / "config.json").read_text())
+    weight_map = {}
+    for shard, members in halves.items():
+        write_safetensors(sharded / shard, {n: f.tensor(n) for n in members})
+        weight_map.update({n: shard for n in members})
+    (sharded / "model.safetensors.index.json").write_text(
+        json.dumps({"metadata": {}, "weight_map": weight_map}))
+    decls = _decls(TINY_B)
+    one = load_checkpoint(whole, decls, "bfloat16", "cpu")
+    two = load_checkpoint(sharded, decls, "bfloat16", "cpu")
+    assert one.offsets == two.offsets
+    assert all(torch.equal(one.view(d.name), two.view(d.name)) for d in decls)
+    # a tensor missing from its shard is named like any other missing tensor
+    del two
+    (sharded / "model-00002-of-00002.safetensors").unlink()
+    write_safetensors(sharded / "model-00002-of-00002.safetensors",
+                      {n: f.tensor(n) for n in halves["model-00002-of-00002.safetensors"][1:]})
+    with pytest.raises(WeightError, match="1 missing"):
+        load_checkpoint(sharded, decls, "bfloat16", "cpu")
+    # a folder with neither a file nor an index says so
+    (tmp_path / "empty").mkdir()
+    with pytest.raises(WeightError, match="neither"):
+        Checkpoint(tmp_path / "empty")
+
+
+def test_names_an_architecture_lets_pass_are_not_unexpected(tmp_path):
+    folder = write_random_model(tmp_path / "m", dict(TINY_A), 0)
+    f = SafetensorsFile(folder / "model.safetensors")
+    tensors = {n: f.tensor(n).clone() for n in f.infos}     # the file is rewritten below
+    del f
+    tensors["model.layers.0.self_attn.rotary_emb.inv_freq"] = torch.ones(8)
+    tensors["model.layers.0.self_attn.stray"] = torch.ones(2)
+    write_safetensors(folder / "model.safetensors", tensors)
+    spec = Qwen2Config.from_dict(TINY_A).model_spec()
+    assert spec.ignore_tensors == ("*.rotary_emb.inv_freq",)
+    with pytest.raises(WeightError) as err:
+        load_checkpoint(folder, _decls(TINY_A), "float32", "cpu", ignore=spec.ignore_tensors)
+    assert "1 unexpected" in str(err.value) and "stray" in str(err.value)
+    assert "inv_freq" not in str(err.value)
+    with pytest.raises(WeightError, match="2 unexpected"):
+        load_checkpoint(folder, _decls(TINY_A), "float32", "cpu")
+
+
+def test_an_arena_the_device_cannot_hold_is_a_typed_error(tmp_path, monkeypatch):
+    """The allocator's failure comes back as `OutOfDeviceMemory` that says what was asked
+    for (`tests/test_emergency_downgrade.py:40-54` of the reference injects the same way)."""
+    from semantic_aware_adaptive_kv_cache_precision_b200 import OutOfDeviceMemory
+    folder = write_random_model(tmp_path / "m", dict(TINY_A), 0)
+    real = torch.empty
+
+    def no_room(*args, **kwargs):
+        if kwargs.get("dtype") == torch.uint8:
+            raise torch.OutOfMemoryError("injected")
+        return real(*args, **kwargs)
+
+    monkeypatch.setattr(torch, "empty", no_room)
+    with pytest.raises(OutOfDeviceMemory, match="the model's weights"):
+        load_checkpoint(folder, _decls(TINY_A), "float32", "cpu")

@@ -57,10 +57,26 @@ def test_static_scratch_entry_point_matches_the_regular_one():
                      len(lengths), heads, kv_heads, d, splits, scale, 0, why, len(why), stream)
         assert code == 0, why.value.decode()
         torch.cuda.synchronize()
-        assert torch.isfinite(got.float()).all()
-        # same kernels, same order of additions: within the tolerance of the kernel tests
-        np.testing.assert_allclose(got.float().cpu().numpy(), want.float().cpu().numpy(),
-                                   rtol=0, atol=1.5e-2, err_msg=f"call {call}")
+        # the same kernels in the same order: the same bits as the entry point that takes
+        # its scratch from the caller
+        assert torch.equal(got, want), f"call {call}: differs from the regular entry point"
+        # and the right answer: each query against a float64 softmax over its sequence's keys,
+        # within the bf16 rounding of the probabilities and of the result
+        q = qkv[:, :heads * d].float().cpu().numpy().astype(np.float64).reshape(-1, heads, d)
+        keys = k_cache.float().cpu().numpy().astype(np.float64)
+        values = v_cache.float().cpu().numpy().astype(np.float64)
+        for i, n in enumerate(lengths):
+            mine = table[i, :-(-n // 64)]
+            k = keys[mine].transpose(0, 2, 1, 3).reshape(-1, kv_heads, d)[:n]
+            v = values[mine].transpose(0, 2, 1, 3).reshape(-1, kv_heads, d)[:n]
+            for h in range(heads):
+                g = h // (heads // kv_heads)
+                s = (k[:, g] @ q[i, h]) * scale
+                p = np.exp(s - s.max())
+                ref = (p / p.sum()) @ v[:, g]
+                np.testing.assert_allclose(got[i, h * d:(h + 1) * d].float().cpu().numpy(), ref,
+                                           rtol=0, atol=1.5e-2,
+                                           err_msg=f"call {call}, sequence {i}, head {h}")
 
     # a problem larger than the built-in scratch is refused, with a sentence, before any launch
     before = got.clone()
