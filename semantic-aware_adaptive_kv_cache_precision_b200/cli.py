@@ -33,37 +33,26 @@ def _engine(args):
                   max_batch=args.max_batch).load_weights()
 
 
-def _tokenizer(model_dir):
-    path = Path(model_dir) / "tokenizer.json"
-    if not path.is_file():
-        raise SystemExit(f"{path} does not exist: give token ids with --prompt-ids")
-    try:
-        from tokenizers import Tokenizer
-    except ImportError:
-        raise SystemExit("the `tokenizers` package is not installed: give token ids with "
-                         "--prompt-ids") from None
-    return Tokenizer.from_file(str(path))
-
-
 def cmd_generate(args) -> int:
     prompts = [_ids(p) for p in args.prompt_ids or []]
     if args.prompt_file:
         prompts += [_ids(line) for line in Path(args.prompt_file).read_text().splitlines()
                     if line.strip()]
-    tokenizer = None
-    if args.prompt:
-        tokenizer = _tokenizer(args.model)
-        prompts += [tokenizer.encode(p).ids for p in args.prompt]
-    if not prompts:
+    if not prompts and not args.prompt:
         raise SystemExit("give --prompt-ids, --prompt-file or --prompt")
     engine = _engine(args)
+    if args.prompt:
+        try:
+            prompts += [engine.encode(p).tolist() for p in args.prompt]
+        except RuntimeError as exc:             # no tokenizer.json, or no `tokenizers` package
+            raise SystemExit(f"{exc}; give token ids with --prompt-ids") from None
     out = engine.generate(prompts, args.new_tokens, stop_at_eos=not args.ignore_eos,
                           temperature=args.temperature, seed=args.seed)
     for i, (tokens, ending) in enumerate(zip(out, engine.endings)):
         record = {"request": i, "tokens": tokens.tolist(), "ending": ending.state,
                   "reason": ending.reason, "positions": ending.positions}
-        if tokenizer is not None:
-            record["text"] = tokenizer.decode(tokens.tolist())
+        if args.prompt:
+            record["text"] = engine.decode(tokens.tolist())
         print(json.dumps(record))
     return 0
 

@@ -1,0 +1,182 @@
+"""The engine at the layer widths it is benchmarked at, against the plain implementation.
+
+The tiny configurations never reach the kernels' real launch shapes: products split over
+thread-block clusters, the down projection left as two sums for the next norm, nine to
+thirty-three key splits folded by groups, an output head of 1,187 row tiles, the fused
+gated product at an intermediate size of 8,960. Here two models have the real widths of
+Qwen2.5-1.5B (two layers, the whole vocabulary, tied head) and of Qwen2.5-7B (one layer, a
+smaller vocabulary, untied head), random weights written as a folder, and the same requests
+run whole, with their last 32 tokens one by one, and in unequal batches one after another in
+a cache that holds one batch: in 32-bit (bit-equal across cuts, within the fp32 bound of the
+plain model) and in bfloat16 (within the bf16 bound). The reference gates its engine on
+whole-model logits in the same way (`tests/test_inference.py:58-66, 101-126`), and its
+gate's constants close the file (`src/microinfer/gate.py:26-28`)."""
+
+import numpy as np
+import pytest
+
+import plain_model as plain
+from helpers import assert_close_to_plain, assert_same_logits
+
+pytestmark = pytest.mark.gpu
+
+WIDE_1P5B = {
+    "architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2",
+    "num_hidden_layers": 2, "hidden_size": 1536, "num_attention_heads": 12,
+    "num_key_value_heads": 2, "intermediate_size": 8960, "vocab_size": 151936,
+    "max_position_embeddings": 4096, "rope_theta": 1000000.0, "rms_norm_eps": 1e-6,
+    "tie_word_embeddings": True, "hidden_act": "silu", "torch_dtype": "bfloat16",
+    "use_sliding_window": False, "eos_token_id": 151645,
+}
+WIDE_7B = {
+    "architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2",
+    "num_hidden_layers": 1, "hidden_size": 3584, "num_attention_heads": 28,
+    "num_key_value_heads": 4, "intermediate_size": 18944, "vocab_size": 20011,
+    "max_position_embeddings": 4096, "rope_theta": 1000000.0, "rms_norm_eps": 1e-6,
+    "tie_word_embeddings": False, "hidden_act": "silu", "torch_dtype": "bfloat16",
+    "use_sliding_window": False, "eos_token_id": 7,
+}
+WIDE = {"1.5b": (WIDE_1P5B, 31), "7b": (WIDE_7B, 32)}
+LENGTHS = [1, 70, 300, 1100]
+
+
+class Wide:
+    """A wide model's folder, its plain tensors, the prompts and the plain logits at the
+    rows that are compared (all rows of the short prompts; of the long ones the first
+    rows, the rows around block boundaries and the last 33)."""
+
+    def __init__(self, name, root):
+        from semantic_aware_adaptive_kv_cache_precision_b200 import write_random_model
+        config, seed = WIDE[name]
+        self.folder = write_random_model(root / f"wide_{name}", dict(config), seed)
+        self.config, self.tensors = plain.read_model_folder(self.folder)
+        rng = np.random.default_rng(seed)
+        self.prompts = [rng.integers(0, config["vocab_size"], n) for n in LENGTHS]
+        self.rows = [self.rows_of(len(p)) for p in self.prompts]
+        self.want = [plain.forward(self.config, self.tensors, p, rows)
+                     for p, rows in zip(self.prompts, self.rows)]
+        self.engines = {}
+
+    @staticmethod
+    def rows_of(n):
+        if n <= 80:
+            return list(range(n))
+        edges = [r for b in range(64, n, 64) for r in (b - 1, b, b + 1)][:18]
+        return sorted(set([0, 1, 2] + edges + list(range(n - 33, n))))
+
+    def engine(self, dtype, **kw):
+        from semantic_aware_adaptive_kv_cache_precision_b200 import Engine
+        key = (dtype, tuple(sorted(kw.items())))
+        if key not in self.engines:
+            kw.setdefault("max_tokens", 2048)
+            self.engines[key] = Engine(self.folder, dtype=dtype, poison_freed=True,
+                                       **kw).load_weights()
+        return self.engines[key]
+
+
+@pytest.fixture(scope="module")
+def wide(tmp_path_factory):
+    root = tmp_path_factory.mktemp("wide")
+    made = {}
+
+    def get(name):
+        if name not in made:
+            made[name] = Wide(name, root)
+        return made[name]
+
+    return get
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["1.5b", "7b"])
+def test_real_widths_whole_stepped_and_batched(name, dtype, wide):
+    model = wide(name)
+    engine = model.engine(dtype)
+    whole = []
+    # 1. each request alone and whole
+    for p, rows, want in zip(model.prompts, model.rows, model.want):
+        (slot,) = engine.open(1)
+        got = engine.step([slot], [p], [rows]).cpu().numpy()
+        engine.close([slot])
+        assert_close_to_plain(got, want, dtype, f"{name} whole, {len(p)} tokens")
+        whole.append(got)
+    # 2. the last 32 tokens one by one (the prompts that are long enough)
+    for p, rows, got_whole in zip(model.prompts, model.rows, whole):
+        if len(p) < 40:
+            continue
+        head = len(p) - 32
+        (slot,) = engine.open(1)
+        engine.step([slot], [p[:head]], [[]])
+        stepped = np.concatenate([engine.step([slot], [p[t:t + 1]]).cpu().numpy()
+                                  for t in range(head, len(p))])
+        engine.close([slot])
+        at = [rows.index(t) for t in range(head, len(p))]
+        assert_same_logits(stepped, got_whole[at], dtype, f"{name} {len(p)} tokens, last 32 stepped")
+    # 3. two unequal batches, one after the other, in a cache that holds one of them; the
+    # prompts go in without their last few tokens, which are decoded, the shorter tails
+    # ending first
+    small = model.engine(dtype, max_tokens=1152 + 128)
+    for members, tails in (([2, 1, 0], [5, 3, 0]), ([3, 1], [4, 7])):
+        prompts = [model.prompts[i] for i in members]
+        heads = [len(p) - t for p, t in zip(prompts, tails)]
+        slots = small.open(len(members))
+        want_rows = [[r for r in model.rows[i] if r < h] for i, h in zip(members, heads)]
+        out = small.step(slots, [p[:h] for p, h in zip(prompts, heads)], want_rows).cpu().numpy()
+        got = {i: {} for i in members}
+        at = 0
+        for i, rows in zip(members, want_rows):
+            for r in rows:
+                got[i][r] = out[at]
+                at += 1
+        fed = dict(zip(members, heads))
+        live = [i for i, p in zip(members, prompts) if fed[i] < len(p)]
+        done = [i for i in members if i not in live]
+        if done:
+            small.close([slots[members.index(i)] for i in done])
+        while live:
+            out = small.step([slots[members.index(i)] for i in live],
+                             [model.prompts[i][fed[i]:fed[i] + 1] for i in live]).cpu().numpy()
+            for row, i in enumerate(live):
+                got[i][fed[i]] = out[row]
+                fed[i] += 1
+            ended = [i for i in live if fed[i] == len(model.prompts[i])]
+            if ended:
+                small.close([slots[members.index(i)] for i in ended])
+                live = [i for i in live if i not in ended]
+            small.cache.check()
+        for i in members:
+            rows = model.rows[i]
+            batched = np.stack([got[i][r] for r in rows])
+            assert_same_logits(batched, whole[i], dtype, f"{name} request {i} in a batch")
+            assert_close_to_plain(batched, model.want[i], dtype, f"{name} request {i} batched")
+        assert small.cache.slots.held == 0
+    if dtype == "bfloat16":
+        assert engine.graph_failure is None and engine._graphs, "decode steps were not replayed"
+
+
+def test_bfloat16_against_the_32_bit_path_at_real_widths(wide):
+    """The gate between the two paths at the benchmark's layer widths: over 230 prefilled
+    positions and eight decode steps of four sequences, the argmax agrees at 99 % of the
+    positions at least (a flip is excused only where the exact path's two largest logits are
+    a near tie) and the mean KL divergence stays below 1e-3."""
+    from semantic_aware_adaptive_kv_cache_precision_b200.gate import compare_logits
+    model = wide("1.5b")
+    rng = np.random.default_rng(5)
+    vocab = model.config["vocab_size"]
+    ids = [rng.integers(0, vocab, n) for n in (128, 37, 64, 1)]
+    tails = [rng.integers(0, vocab, 8) for _ in ids]
+
+    def logits_of(engine):
+        slots = engine.open(len(ids))
+        rows = [engine.step(slots, ids, [list(range(len(i))) for i in ids]).cpu().numpy()]
+        for t in range(8):
+            rows.append(engine.step(slots, [tail[t:t + 1] for tail in tails]).cpu().numpy())
+        engine.close(slots)
+        return np.concatenate(rows)
+
+    report = compare_logits(logits_of(model.engine("bfloat16")), logits_of(model.engine("float32")))
+    print(report)
+    assert report["positions"] == 262
+    assert report["hard_flips"] == 0 and report["top1_agreement"] >= 0.99, report
+    assert report["mean_kl"] < 1e-3, report
+    assert report["max_diff_over_std"] < 6e-2, report

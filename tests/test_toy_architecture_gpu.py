@@ -392,3 +392,177 @@ def test_routed_feed_forward_and_another_position_encoding(tmp_path):
     engine.close(slots)
     for i in range(3):
         assert np.abs(np.concatenate(rows[i]) - want[i]).max() <= 5e-5 * np.abs(want[i]).max()
+
+
+# ---- a third toy: keys and values of different widths, and the model-level hooks --------------
+# A mixer that caches keys of width 8 and values of width 20 for each position (its cache
+# need says so; the cache gives it storage of that shape), beside the package's attention in
+# one model whose spec scales the embedding, scales and soft-caps the logits, has a bias on
+# its output head, and lets a checkpoint carry a buffer that no part reads.
+
+@dataclass(frozen=True)
+class NarrowKeySpec:
+    hidden: int
+    key_dim: int
+    value_dim: int
+    kind: str = "toy_narrow_keys"
+
+
+class NarrowKeyMixer(Part):
+    """out_t = W_o sum_{j <= t} softmax_j(q_t . k_j / sqrt(dk)) v_j with k of width dk and v
+    of width dv: one KV head, no position encoding."""
+
+    graph_safe = False      # its launches depend on the sequences' lengths on the host
+
+    def tensor_decls(self):
+        s, p = self.spec, self.prefix
+        return [TensorDecl(p + "q.weight", (s.key_dim, s.hidden)),
+                TensorDecl(p + "k.weight", (s.key_dim, s.hidden)),
+                TensorDecl(p + "v.weight", (s.value_dim, s.hidden)),
+                TensorDecl(p + "o.weight", (s.hidden, s.value_dim))]
+
+    def bind(self, arena):
+        p = self.prefix
+        self.wq, self.wk, self.wv, self.wo = (arena.view(p + n + ".weight").float()
+                                              for n in "qkvo")
+
+    def cache_need(self):
+        from semantic_aware_adaptive_kv_cache_precision_b200.cache import KVNeed
+        return KVNeed(1, self.spec.key_dim, value_dim=self.spec.value_dim, dtype="float32")
+
+    def forward(self, h, step, view, residual, write_cache=True):
+        h = h.float()
+        q, k, v = h @ self.wq.t(), h @ self.wk.t(), h @ self.wv.t()
+        assert view.keys.shape[1:] == (1, 64, self.spec.key_dim)
+        assert view.values.shape[1:] == (1, 64, self.spec.value_dim)
+        seq, pos = step.token_seq.long(), step.positions.long()
+        block = view.block_table[seq, pos // 64].long()
+        if write_cache:
+            view.keys[block, 0, pos % 64] = k
+            view.values[block, 0, pos % 64] = v
+        out = torch.empty_like(v)
+        at = 0
+        for i, (start, count) in enumerate(zip(step.starts, step.new_counts)):
+            blocks = view.block_table[i, :-(-(start + count) // 64)].long()
+            keys = view.keys[blocks, 0].reshape(-1, self.spec.key_dim)[:start + count]
+            values = view.values[blocks, 0].reshape(-1, self.spec.value_dim)[:start + count]
+            scores = q[at:at + count] @ keys.t() / self.spec.key_dim ** 0.5
+            seen = torch.arange(start + count, device=h.device)[None, :] <= \
+                (start + torch.arange(count, device=h.device))[:, None]
+            out[at:at + count] = torch.softmax(scores.masked_fill(~seen, float("-inf")), -1) @ values
+            at += count
+        residual += out @ self.wo.t()
+
+
+register_part("toy_narrow_keys", NarrowKeyMixer)
+
+
+@dataclass(frozen=True)
+class HookedConfig:
+    hidden_size: int = 64
+    key_dim: int = 8
+    value_dim: int = 20
+    num_attention_heads: int = 2
+    intermediate_size: int = 56
+    vocab_size: int = 97
+    rms_norm_eps: float = 1e-5
+    max_position_embeddings: int = 192
+    embed_scale: float = 2.0
+    logit_scale: float = 0.5
+    logit_softcap: float = 2.0
+
+    @classmethod
+    def from_dict(cls, raw):
+        return cls(**{k: raw[k] for k in cls.__dataclass_fields__ if k in raw})
+
+    def to_dict(self):
+        return {**self.__dict__, "architectures": ["ToyHookedForTests"]}
+
+    def model_spec(self):
+        h, d = self.hidden_size, self.hidden_size // self.num_attention_heads
+        norm = NormSpec(h, self.rms_norm_eps)
+        mlp = GatedMLPSpec(h, self.intermediate_size, "silu")
+        attn = AttentionSpec(hidden=h, heads=self.num_attention_heads, kv_heads=1, head_dim=d,
+                             qkv_bias=True, out_bias=False, scale=d ** -0.5, window=None,
+                             position=RotarySpec(d, d, 1e4, self.max_position_embeddings))
+        blocks = (BlockSpec("model.layers.0.", NarrowKeySpec(h, self.key_dim, self.value_dim),
+                            norm, mlp, norm, mixer_name="mixer"),
+                  BlockSpec("model.layers.1.", attn, norm, mlp, norm))
+        return ModelSpec(architecture="ToyHookedForTests", vocab_size=self.vocab_size, hidden=h,
+                         blocks=blocks, run_order=(LayerCall(0, 0), LayerCall(1, 1)),
+                         final_norm=norm, tie_head=False,
+                         max_positions=self.max_position_embeddings, stored_dtype="float32",
+                         init_std=0.1, embed_scale=self.embed_scale,
+                         logit_scale=self.logit_scale, logit_softcap=self.logit_softcap,
+                         head_bias_name="lm_head.bias", ignore_tensors=("*.unused_buffer",))
+
+
+sakv.register_architecture("ToyHookedForTests", HookedConfig)
+
+
+def plain_hooked(config: HookedConfig, t: dict, ids) -> np.ndarray:
+    n = len(ids)
+    heads = config.num_attention_heads
+    d = config.hidden_size // heads
+    eps = config.rms_norm_eps
+    x = plain.embed(t["model.embed_tokens.weight"], ids) * config.embed_scale
+    p = "model.layers.0."
+    h = plain.rms_norm(x, t[p + "input_layernorm.weight"], eps)
+    q, k, v = (h @ t[p + f"mixer.{n_}.weight"].T for n_ in "qkv")
+    s = np.where(plain.causal_mask(n), q @ k.T / np.sqrt(config.key_dim), -np.inf)
+    x = x + (plain.softmax(s) @ v) @ t[p + "mixer.o.weight"].T
+    w = {k_[len(p + "mlp."):]: v_ for k_, v_ in t.items() if k_.startswith(p + "mlp.")}
+    x = x + plain.swiglu_mlp(plain.rms_norm(x, t[p + "post_attention_layernorm.weight"], eps), w)
+    raw = {"num_hidden_layers": 2, "hidden_size": config.hidden_size, "num_attention_heads": heads,
+           "num_key_value_heads": 1, "rope_theta": 1e4, "rms_norm_eps": eps}
+    x = plain.decoder_layer(x, t, raw, 1, np.arange(n))
+    logits = plain.rms_norm(x, t["model.norm.weight"], eps) @ t["lm_head.weight"].T
+    logits = (logits + t["lm_head.bias"]) * config.logit_scale
+    return config.logit_softcap * np.tanh(logits / config.logit_softcap)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_keys_and_values_of_different_widths_and_the_models_hooks(dtype, tmp_path):
+    from semantic_aware_adaptive_kv_cache_precision_b200.weights import (SafetensorsFile,
+                                                                          write_safetensors)
+    config = HookedConfig()
+    folder = sakv.write_random_model(tmp_path / "hooked", config, seed=11)
+    f = SafetensorsFile(folder / "model.safetensors")
+    tensors = {n: f.tensor(n).clone() for n in f.infos}
+    del f
+    assert tensors["lm_head.bias"].abs().sum() == 0           # written as zeros: make it matter
+    tensors["lm_head.bias"] = torch.linspace(-2, 2, config.vocab_size)
+    tensors["model.layers.0.mixer.unused_buffer"] = torch.ones(3)   # let pass by the spec
+    write_safetensors(folder / "model.safetensors", tensors)
+    engine = sakv.Engine(folder, dtype=dtype, max_tokens=1024, poison_freed=True).load_weights()
+    needs = engine.model.cache_needs()
+    assert needs[0].head_dim == 8 and needs[0].value_dim == 20 and needs[1].value_dim is None
+    _, plain_tensors = plain.read_model_folder(folder)
+    rng = np.random.default_rng(2)
+    prompts = [rng.integers(0, config.vocab_size, n) for n in (70, 3, 130)]
+    want = [plain_hooked(config, plain_tensors, p) for p in prompts]
+    assert max(np.abs(w).max() for w in want) > 1.5           # the cap (2.0) bends something
+    tol = 2e-5 if dtype == "float32" else 0.06
+    for p, w in zip(prompts, want):
+        scale = np.abs(w).max() if dtype == "float32" else w.std()
+        assert np.abs(engine.forward(p) - w).max() <= tol * scale
+    group = engine.cache.groups[engine.cache.entry_group[0][0]]
+    assert group.keys.shape[-1] == 8 and group.values.shape[-1] == 20
+    assert group.keys.dtype == torch.float32
+    # an unequal batch with the last tokens one by one, twice, so that blocks are used again
+    for _ in range(2):
+        slots = engine.open(3)
+        heads = [len(p) - 2 for p in prompts]
+        out = engine.step(slots, [p[:h] for p, h in zip(prompts, heads)],
+                          [list(range(h)) for h in heads]).cpu().numpy()
+        rows = [[out[sum(heads[:i]):sum(heads[:i + 1])]] for i in range(3)]
+        for t_ in range(2):
+            step_out = engine.step(slots, [p[h + t_:h + t_ + 1] for p, h in zip(prompts, heads)])
+            for i in range(3):
+                rows[i].append(step_out[i:i + 1].cpu().numpy())
+        engine.close(slots)
+        for i in range(3):
+            scale = np.abs(want[i]).max() if dtype == "float32" else want[i].std()
+            assert np.abs(np.concatenate(rows[i]) - want[i]).max() <= tol * scale, f"request {i}"
+    engine.cache.check()
+    assert engine.graph_failure is None and not engine.model.graph_safe
