@@ -113,6 +113,82 @@ rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ add,
     o[i] = narrow<Out>(in[i] * scale * widen(weight[i]));
 }
 
+// The same for MANY rows in bfloat16 (a prefill step): a warp takes a row at a time and keeps
+// it in registers, a lane every 32nd group of four floats, so that a warp's access is 512
+// contiguous bytes; the sum of squares needs shuffles only, no block-wide barrier; and the
+// grid is sized to the GPU and walks the rows, so that no wave is left half full. (One block a
+// row, as above, took 12.0 us for 2,048 rows of 1,536 with a sum to fold: 44 MB at 3.7 TB/s.)
+// The order of a row's additions depends on its length alone. `kPer`: groups of four a lane
+// holds, hidden <= 128 * kPer.
+template <int kPer, bool kAdd>
+__global__ void __launch_bounds__(256)
+rmsnorm_rows_kernel(float* __restrict__ x, const float* __restrict__ add, int parts,
+                    long long part_stride, const int32_t* __restrict__ rows,
+                    const __nv_bfloat16* __restrict__ weight, __nv_bfloat16* __restrict__ out,
+                    int n_rows, int hidden, float eps) {
+  let_next_kernel_start();
+  wait_for_previous_kernel();
+  const int lane = threadIdx.x & 31;
+  const int warps = (gridDim.x * blockDim.x) >> 5;
+  const int groups = hidden >> 2;                       // float4 groups of a row
+  for (int r = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; r < n_rows; r += warps) {
+    const long long src = rows ? rows[r] : r;
+    float* in = x + src * hidden;
+    float4 v[kPer];
+    float acc = 0.f;
+#pragma unroll
+    for (int i = 0; i < kPer; ++i) {
+      const int g = lane + 32 * i;
+      v[i] = g < groups ? reinterpret_cast<const float4*>(in)[g] : make_float4(0, 0, 0, 0);
+    }
+    if (kAdd) {
+      const float* more = add + src * hidden;
+#pragma unroll
+      for (int i = 0; i < kPer; ++i) {
+        const int g = lane + 32 * i;
+        if (g < groups) {
+          float4 sum = reinterpret_cast<const float4*>(more)[g];
+          for (int s = 1; s < parts; ++s) {
+            const float4 a = reinterpret_cast<const float4*>(more + s * part_stride)[g];
+            sum.x += a.x; sum.y += a.y; sum.z += a.z; sum.w += a.w;
+          }
+          v[i].x += sum.x; v[i].y += sum.y; v[i].z += sum.z; v[i].w += sum.w;
+          reinterpret_cast<float4*>(in)[g] = v[i];
+        }
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < kPer; ++i)
+      acc += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
+    const float scale = rsqrtf(warp_sum(acc) / static_cast<float>(hidden) + eps);
+    __nv_bfloat16* o = out + (long long)r * hidden;
+#pragma unroll
+    for (int i = 0; i < kPer; ++i) {
+      const int g = lane + 32 * i;
+      if (g < groups) {
+        float w[4];
+        load4(weight + 4 * g, w);
+        store4(o + 4 * g, v[i].x * scale * w[0], v[i].y * scale * w[1], v[i].z * scale * w[2],
+               v[i].w * scale * w[3]);
+      }
+    }
+  }
+}
+
+template <int kPer>
+int launch_rows(float* x, const float* add, int parts, long long part_stride, const int32_t* rows,
+                const __nv_bfloat16* weight, __nv_bfloat16* out, int n_rows, int hidden, float eps,
+                cudaStream_t stream) {
+  const int blocks = min((n_rows + 7) / 8, sm_count() * 8);
+  if (add)
+    return launch_overlapped(rmsnorm_rows_kernel<kPer, true>, dim3(blocks), dim3(256), 0, stream, 1,
+                             x, add, parts, part_stride, rows, weight, out, n_rows, hidden, eps);
+  return launch_overlapped(rmsnorm_rows_kernel<kPer, false>, dim3(blocks), dim3(256), 0, stream, 1,
+                           x, add, parts, part_stride, rows, weight, out, n_rows, hidden, eps);
+}
+
+constexpr int kManyRows = 256;     // from here on the warp-a-row kernel runs (bfloat16 only)
+
 }  // namespace
 
 // `add`: null, or `parts` fp32 tensors [n_rows, hidden], `part_stride` elements apart, that
@@ -124,6 +200,19 @@ SAKV_EXPORT int sakv_rmsnorm(float* x, const float* add, int parts, long long pa
     return cudaErrorInvalidValue;
   if (n_rows == 0) return 0;
   const int threads = kThreads;
+  // Many rows in bfloat16: a warp a row. (The 32-bit path keeps the kernel above for every
+  // count of rows, so that a row's result never depends on how many rows came with it.)
+  if (n_rows >= kManyRows && weight_dtype == SAKV_BF16 && out_dtype == SAKV_BF16 &&
+      (hidden & 127) == 0 && hidden <= 128 * 32 &&
+      !((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(add) |
+         reinterpret_cast<uintptr_t>(weight) | reinterpret_cast<uintptr_t>(out)) & 15) &&
+      (part_stride & 3) == 0) {
+    const __nv_bfloat16* w = (const __nv_bfloat16*)weight;
+    __nv_bfloat16* o = (__nv_bfloat16*)out;
+    if (hidden <= 128 * 16)
+      return launch_rows<16>(x, add, parts, part_stride, rows, w, o, n_rows, hidden, eps, stream);
+    return launch_rows<32>(x, add, parts, part_stride, rows, w, o, n_rows, hidden, eps, stream);
+  }
   if (add) {
     if ((reinterpret_cast<uintptr_t>(add) & 15) || weight_dtype != SAKV_BF16 ||
         out_dtype != SAKV_BF16)

@@ -55,6 +55,40 @@ def test_rms_norm(hidden, wdtype, odtype):
                                plain.rms_norm(host(tiny), host(w), 1e-2), rtol=1e-5)
 
 
+@pytest.mark.parametrize("hidden", [128, 1536, 2048, 3584, 4096, 200])
+@pytest.mark.parametrize("parts", [0, 1, 3])
+def test_rms_norm_of_many_rows(hidden, parts):
+    """From 256 rows on, bf16 norms run a warp a row (hidden a multiple of 128, up to 4,096;
+    other sizes keep the block-a-row kernel): against float64, with a sum of `parts` products
+    folded into the stream on the way, with a gather of rows, and equal to the bit to what
+    the few-rows kernel gives each row by itself."""
+    rng = np.random.default_rng(hidden + parts)
+    n = 300
+    x = dev(rng.standard_normal((n, hidden)) * 2.0)
+    w = dev(1 + 0.1 * rng.standard_normal(hidden), torch.bfloat16)
+    eps = 1e-6
+    if parts:
+        add = dev(rng.standard_normal((parts, n, hidden)))
+        total = host(x) + host(add).sum(0)
+        stream = x.clone()
+        got = ops.rms_norm(stream, w, eps, torch.bfloat16, add=add if parts > 1 else add[0])
+        np.testing.assert_allclose(host(stream), total, rtol=1e-6, atol=1e-6)    # x keeps the sum
+        few = x[:5].clone()
+        part = add[:, :5].contiguous()
+        ops.rms_norm(few, w, eps, torch.bfloat16, add=part if parts > 1 else part[0])
+        assert torch.equal(few, stream[:5])         # the same sum, in the same order
+    else:
+        total = host(x)
+        got = ops.rms_norm(x, w, eps, torch.bfloat16)
+        rows = torch.as_tensor(rng.permutation(n)[:280].astype(np.int32)).to(DEV)
+        picked = ops.rms_norm(x, w, eps, torch.bfloat16, rows=rows)
+        assert torch.equal(picked, got[rows.long()])
+    # (the fp32 sums of up to four terms of size <= 10 are off by up to 4 * 2^-24 * 10, which
+    # an element that cancels to nearly nothing shows as a large RELATIVE error: hence the atol)
+    np.testing.assert_allclose(host(got), plain.rms_norm(total, host(w), eps),
+                               rtol=2 * ULP[torch.bfloat16], atol=3e-6)
+
+
 def make_cache(rng, n_blocks, kv_heads, head_dim, dtype):
     k = dev(rng.standard_normal((n_blocks, kv_heads, ops.CACHE_BLOCK, head_dim)), dtype)
     v = dev(rng.standard_normal((n_blocks, kv_heads, ops.CACHE_BLOCK, head_dim)), dtype)
