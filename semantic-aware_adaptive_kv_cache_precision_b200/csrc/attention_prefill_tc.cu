@@ -359,26 +359,45 @@ __global__ void fold_partials_kernel(const int4* __restrict__ folds, const float
   const int h = blockIdx.y;
   const int r = (blockIdx.x % (QT / kFoldRows)) * kFoldRows + (threadIdx.x >> 5);   // a warp per row
   if (r < f.w) {
+    // A lane takes four of the row's 128 sizes (one 16-byte read a partial); the partials
+    // are taken four at a time with every read of a round in flight together, so that a fold
+    // of up to four partials costs one round trip for the maxima and sums and one for the
+    // outputs. Rounds are merged like tiles of an online softmax, always in order.
     const int lane = threadIdx.x & 31;
-    float big = -INFINITY;
-    for (int s = 0; s < f.y; ++s)
-      big = fmaxf(big, part_ml[(((long long)(f.x + s) * heads + h) * QT + r) * 2]);
-    const float use = (big == -INFINITY) ? 0.f : big;
-    float total = 0.f;
-    float acc[D / 32];
+    constexpr int kRound = 4;
+    float big = -INFINITY, total = 0.f;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s0 = 0; s0 < f.y; s0 += kRound) {
+      float2 ml[kRound];
+      float4 o[kRound];
 #pragma unroll
-    for (int i = 0; i < D / 32; ++i) acc[i] = 0.f;
-    for (int s = 0; s < f.y; ++s) {
-      const long long slot = ((long long)(f.x + s) * heads + h) * QT + r;
-      const float w = mma::exp2_fast(part_ml[slot * 2] - use);
-      total += w * part_ml[slot * 2 + 1];
+      for (int j = 0; j < kRound; ++j) {
+        const bool live = s0 + j < f.y;
+        const long long slot = ((long long)(f.x + s0 + (live ? j : 0)) * heads + h) * QT + r;
+        ml[j] = live ? *reinterpret_cast<const float2*>(part_ml + slot * 2)
+                     : make_float2(-INFINITY, 0.f);
+        o[j] = live ? *reinterpret_cast<const float4*>(part_o + slot * D + lane * 4)
+                    : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+      float top = big;
 #pragma unroll
-      for (int i = 0; i < D / 32; ++i) acc[i] += w * part_o[slot * D + i * 32 + lane];
+      for (int j = 0; j < kRound; ++j) top = fmaxf(top, ml[j].x);
+      if (top == -INFINITY) continue;
+      const float keep = mma::exp2_fast(big - top);          // 0 the first time
+      total *= keep;
+      acc.x *= keep; acc.y *= keep; acc.z *= keep; acc.w *= keep;
+      big = top;
+#pragma unroll
+      for (int j = 0; j < kRound; ++j) {
+        const float w = mma::exp2_fast(ml[j].x - big);       // 0 for a partial that saw no key
+        total += w * ml[j].y;
+        acc.x += w * o[j].x; acc.y += w * o[j].y; acc.z += w * o[j].z; acc.w += w * o[j].w;
+      }
     }
-    const float inv = 1.f / total;
-    __nv_bfloat16* dst = out + ((long long)(f.z + r) * heads + h) * D;
-#pragma unroll
-    for (int i = 0; i < D / 32; ++i) dst[i * 32 + lane] = __float2bfloat16_rn(acc[i] * inv);
+    const float inv = total > 0.f ? 1.f / total : 0.f;
+    __nv_bfloat16* dst = out + ((long long)(f.z + r) * heads + h) * D + lane * 4;
+    *reinterpret_cast<uint2*>(dst) = make_uint2(mma::pack_bf16(acc.x * inv, acc.y * inv),
+                                                mma::pack_bf16(acc.z * inv, acc.w * inv));
   }
 }
 
