@@ -10,9 +10,24 @@ import torch
 
 from ._lib import KernelError, call, plain_function, ptr
 
-#: from this many tokens on the fused kernel beats the library's product followed by the
-#: activation kernel (measured: equal at 512, 86.5 against 92.4 us at 2,048)
-MIN_TOKENS = 1024
+TILE_TOKENS, TILE_ROWS = 256, 128      # a block's tile: 256 tokens x (128 gate + 128 up) rows
+
+
+def worth_it(tokens: int, inter: int, sms: int | None = None) -> bool:
+    """Whether the fused kernel beats the library's product followed by the activation
+    kernel for `tokens` tokens. Its time goes by whole waves of tiles and whole tiles of 256
+    tokens, the library's by the tokens, so it wins where both are well filled. Measured with
+    cold weights, fused against library (us): 1536 -> 2 x 8960: 256 tokens 31.6 / 27.6 (70
+    tiles, half a wave), 512: 33.6 / 33.8, 768: 50.0 / 44.0 (1.4 waves), 1,024: 51.2 / 56.3,
+    2,048: 86.5 / 92.4; 3584 -> 2 x 18944: 256 tokens 68.6 / 84.9 (148 tiles, one wave), 384:
+    98.3 / 87.0 (half-empty token tiles), 1,024: 178 / 181, 1,500: 258 / 282."""
+    from ._lib import sm_count
+    sms = sms or sm_count()
+    token_tiles = -(-tokens // TILE_TOKENS)
+    tiles = token_tiles * -(-inter // TILE_ROWS)
+    waves = -(-tiles // sms)
+    return tokens > 64 and tiles >= 0.85 * waves * sms and tokens >= 0.8 * token_tiles * TILE_TOKENS
+
 
 _weight_maps: dict = {}
 

@@ -637,8 +637,14 @@ def test_gated_product_for_many_tokens(M, I, K):
     assert np.abs(got - want).max() <= 2.0 ** -8 * (np.abs(want).max() + 1) * 1.5
     twin = host(ops.gated_silu(torch.mm(x, w.t())))
     assert np.abs(got - twin).max() <= 2.0 ** -7 * (np.abs(want).max() + 1)
-    if M >= gemm_wide.MIN_TOKENS:
+    if gemm_wide.worth_it(M, I):
         assert torch.equal(ops.gated_up(x, w), gemm_wide.gated(x, w))    # the product path takes it
+    assert gemm_wide.worth_it(2048, 8960, sms=148) and gemm_wide.worth_it(512, 8960, sms=148)
+    assert gemm_wide.worth_it(256, 18944, sms=148)              # 148 tiles: one full wave
+    assert not gemm_wide.worth_it(256, 8960, sms=148)           # 70 tiles: half a wave
+    assert not gemm_wide.worth_it(768, 8960, sms=148)           # 210 tiles: 1.4 waves
+    assert not gemm_wide.worth_it(300, 18944, sms=148)          # token tiles 59 % full
+    assert not gemm_wide.worth_it(64, 18944, sms=148)
 
 
 def test_linear_hands_back_k_ranges_only_when_asked():
