@@ -370,6 +370,10 @@ def main() -> int:
     ap.add_argument("--context", type=int, default=CONTEXT, help="cached tokens per sequence")
     ap.add_argument("--points", default="1,64", help="further batch sizes to decode at")
     ap.add_argument("--no-points", action="store_true", help="skip the further batch sizes")
+    ap.add_argument("--tc-max-tokens", type=int, default=None,
+                    help="steps of up to this many tokens run the library's own tcgen05 "
+                         "products (default: the library's setting, 64); 0 sends every "
+                         "product to cuBLAS, for comparing the two inside the step")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-check", action="store_true",
                     help="skip the comparison of the bf16 logits with the fp32 path's")
@@ -390,6 +394,11 @@ def main() -> int:
     from semantic_aware_adaptive_kv_cache_precision_b200 import sampling
     from semantic_aware_adaptive_kv_cache_precision_b200.ops import _lib
 
+    if args.tc_max_tokens is not None:
+        import importlib
+        importlib.import_module(
+            "semantic_aware_adaptive_kv_cache_precision_b200.ops.linear").TC_MAX_TOKENS = \
+            args.tc_max_tokens
     model_name, sizes = SHAPES[args.shape]
     raw = {**QWEN25_1P5B, **sizes}
     full_layers = raw["num_hidden_layers"]
@@ -572,6 +581,7 @@ def main() -> int:
                    "vocab": cfg.vocab_size, "tied_head": cfg.tie_word_embeddings,
                    "global_batch": args.batch, "seq_len": context, "new_tokens": K,
                    "parallelism": "single GPU", "l2": f"weights ({weight_gb:.1f} GB) exceed L2; no flush",
+                   "tc_max_tokens": args.tc_max_tokens if args.tc_max_tokens is not None else 64,
                    "peaks": pk["source"]},
         "prefill": prefill,
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"],
