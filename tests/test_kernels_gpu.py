@@ -441,6 +441,39 @@ def test_attention_decode_kernel(heads, kv_heads, d, window, splits):
     np.testing.assert_allclose(host(got), host(plain_out), rtol=0, atol=2e-2)
 
 
+@pytest.mark.parametrize("splits", [1, 3])
+@pytest.mark.parametrize("rotary", [False, True])
+def test_attention_decode_with_lengths_it_cannot_serve(splits, rotary):
+    """A sequence whose length is 0, negative or beyond its block list (the engine never
+    passes one; a caller of the exported function might) gets zeros, reads nothing outside
+    the tables and writes nothing into the cache; its neighbours in the batch are served."""
+    heads, kv_heads, d = 4, 2, 64
+    rng = np.random.default_rng(9)
+    good = [70, 1, 200]
+    k_cache, v_cache, table = paged_case(rng, good + [64, 64, 64], kv_heads, d)
+    lengths = good + [0, -5, table.shape[1] * 64 + 1]
+    B = len(lengths)
+    qkv = dev(rng.standard_normal((B, (heads + 2 * kv_heads) * d)), torch.bfloat16)
+    j = np.arange(d // 2)
+    angle = np.arange(256)[:, None] * np.power(1e4, -2.0 * j / d)[None, :]
+    tables = (dev(np.cos(angle)), dev(np.sin(angle))) if rotary else None
+    k_before, v_before = k_cache.clone(), v_cache.clone()
+    lens, tab = dev(lengths, torch.int32), dev(table, torch.int32)
+    got = ops.attention_decode(qkv, k_cache, v_cache, lens, tab, heads, kv_heads, d, d ** -0.5,
+                               None, 256, splits=splits, rotary=tables)
+    assert all(v == 0 for v in ops.kernel_errors().values())
+    assert torch.count_nonzero(got[len(good):]) == 0 and torch.isfinite(got.float()).all()
+    want = ops.attention_decode(qkv[:3].contiguous(), k_before.clone(), v_before.clone(), lens[:3].contiguous(),
+                                tab[:3].contiguous(), heads, kv_heads, d, d ** -0.5, None, 256,
+                                splits=splits, rotary=tables)
+    assert torch.equal(got[:3], want)
+    for now, was, blocks in ((k_cache, k_before, table), (v_cache, v_before, table)):
+        for i in range(len(good), B):          # the blocks of the unserved sequences: untouched
+            mine = torch.as_tensor(blocks[i][blocks[i] >= 0], device=DEV, dtype=torch.long)
+            a, b = now[mine], was[mine]
+            assert torch.equal(torch.nan_to_num(a.float()), torch.nan_to_num(b.float()))
+
+
 @pytest.mark.parametrize("heads,kv_heads,d,window,splits", [
     (12, 2, 128, None, None), (12, 2, 128, None, 1), (2, 1, 64, None, 3), (6, 6, 64, 70, None),
     (7, 1, 128, 200, 5), (16, 1, 128, None, 2)])
