@@ -179,15 +179,13 @@ def choose(logits: torch.Tensor, temperature: float = 0.0, seed: int = 0,
     out = torch.empty((rows,), dtype=torch.int32, device=logits.device)
     chunks = plain_function("sakv_choose_chunks")(vocab)
     scratch = _choose_scratch.get(logits.device)
-    if scratch is None or scratch[0].numel() < rows * chunks or scratch[2].numel() < rows:
-        size = max(rows * chunks, 4096)
-        scratch = (torch.empty(size, dtype=torch.float32, device=logits.device),
-                   torch.empty(size, dtype=torch.int32, device=logits.device),
+    if scratch is None or scratch[0].numel() < rows * chunks or scratch[1].numel() < rows:
+        scratch = (torch.empty(max(rows * chunks, 4096), dtype=torch.int64, device=logits.device),
                    torch.zeros(max(rows, 1024), dtype=torch.int32, device=logits.device))
         _choose_scratch[logits.device] = scratch
     call("sakv_choose", ptr(logits), logits.stride(0) if rows else vocab, rows, vocab,
          float(temperature), int(seed) & 0xFFFFFFFFFFFFFFFF, ptr(request), ptr(step), ptr(out),
-         ptr(scratch[0]), ptr(scratch[1]), ptr(scratch[2]))
+         ptr(scratch[0]), ptr(scratch[1]))
     return out
 
 

@@ -30,7 +30,7 @@ SIGNATURES = {
     "sakv_attention_plain": ("attention_plain",
                              [P, I, L, P, P, P, P, P, P, I, I, I, I, I, F, I, P]),
     "sakv_gemm_f32": ("gemm_f32", [P, L, P, P, P, L, I, I, I, I, P]),
-    "sakv_choose": ("sampling", [P, L, I, I, F, U, P, P, P, P, P, P, P]),
+    "sakv_choose": ("sampling", [P, L, I, I, F, U, P, P, P, P, P, P]),
     "sakv_decode_attention": ("attention_decode",
                               [P, P, P, L, P, P, I, P, P, P, I, I, I, I, I, F, I, P, P, I, P, P, P]),
     "sakv_prefill_attention": ("attention_prefill",

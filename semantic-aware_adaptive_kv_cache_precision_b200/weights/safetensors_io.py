@@ -56,8 +56,9 @@ class SafetensorsFile:
                 raise WeightError(f"{self.path}: {size} bytes is too short for a safetensors file")
             (length,) = struct.unpack("<Q", head)
             if length <= 0 or length > 100_000_000 or 8 + length > size:
-                raise WeightError(f"{self.path}: implausible header length {length}; "
-                                  "not a safetensors file")
+                raise WeightError(f"{self.path}: its first eight bytes announce a header of "
+                                  f"{length} bytes, which a safetensors file of {size} bytes "
+                                  "cannot have")
             try:
                 header = json.loads(f.read(length))
             except (json.JSONDecodeError, UnicodeDecodeError):
@@ -89,8 +90,8 @@ class SafetensorsFile:
             raise WeightError(f"{self.path} has a bad header:\n" + "\n".join(problems))
         needed = self.base + max((i.end for i in self.infos.values()), default=0)
         if size < needed:
-            raise WeightError(f"{self.path.name} is truncated: {size:,} bytes on disk, "
-                              f"{needed:,} expected from the header")
+            raise WeightError(f"{self.path.name} is cut short: its header places tensors up to "
+                              f"byte {needed:,}, the file ends at byte {size:,}")
         self._map = None
 
     def _mapped(self):

@@ -38,7 +38,7 @@ def test_broken_files_are_named(tmp_path):
     with pytest.raises(WeightError, match="too short"):
         SafetensorsFile(p)
     p.write_bytes(struct.pack("<Q", 10 ** 12) + b"{}")
-    with pytest.raises(WeightError, match="implausible header"):
+    with pytest.raises(WeightError, match="announce a header"):
         SafetensorsFile(p)
     p.write_bytes(struct.pack("<Q", 4) + b"nope")
     with pytest.raises(WeightError, match="not JSON"):
@@ -46,7 +46,7 @@ def test_broken_files_are_named(tmp_path):
     write_safetensors(p, {"w": torch.randn(8, 8)})
     data = p.read_bytes()
     p.write_bytes(data[:-40])
-    with pytest.raises(WeightError, match="truncated"):
+    with pytest.raises(WeightError, match="cut short"):
         SafetensorsFile(p)
     header = json.dumps({"w": {"dtype": "F8_E4M3", "shape": [2], "data_offsets": [0, 2]}}).encode()
     p.write_bytes(struct.pack("<Q", len(header)) + header + b"\0\0")
