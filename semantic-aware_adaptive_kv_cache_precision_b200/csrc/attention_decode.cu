@@ -508,17 +508,11 @@ int launch(const CUtensorMap* k_map, const CUtensorMap* v_map, const __nv_bfloat
            int kv_heads, int splits, float scale, int window, const float* cos_t,
            const float* sin_t, int rotary_rows, __nv_bfloat16* k_out, __nv_bfloat16* v_out,
            cudaStream_t stream) {
-  // a kernel's attributes belong to a device: set once on each device that launches it
-  constexpr int kDevices = 64;
-  static bool configured_on[kDevices] = {};
-  int device = 0;
-  if (cudaGetDevice(&device) != cudaSuccess) return cudaErrorInvalidValue;
-  const bool remember = device >= 0 && device < kDevices;
-  const bool configured = remember && configured_on[device];
+  static PerDeviceOnce configured;      // (attributes are per device)
   int* error = nullptr;
   if (cudaGetSymbolAddress(reinterpret_cast<void**>(&error), g_error) != cudaSuccess)
     return cudaErrorInvalidValue;
-  if (!configured) {
+  if (configured.needs()) {
     cudaError_t e = cudaFuncSetAttribute(decode_attention_kernel<D>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          Smem<D>::kBytes);
@@ -527,7 +521,7 @@ int launch(const CUtensorMap* k_map, const CUtensorMap* v_map, const __nv_bfloat
                                cudaFuncAttributePreferredSharedMemoryCarveout,
                                cudaSharedmemCarveoutMaxShared);
     if (e != cudaSuccess) return static_cast<int>(e);
-    if (remember) configured_on[device] = true;
+    configured.done();
   }
   const dim3 grid(splits, kv_heads, sequences);
   int status = launch_overlapped(decode_attention_kernel<D>, grid, dim3(kThreads), Smem<D>::kBytes,

@@ -261,11 +261,11 @@ int launch(const CUtensorMap* k_map, const CUtensorMap* v_map, const __nv_bfloat
            long long q_stride, __nv_bfloat16* out, const int4* q_tiles, int n_tiles,
            const int32_t* seq_lens, const int32_t* block_table, int max_blocks, int heads,
            int kv_heads, float scale, int window, cudaStream_t stream) {
-  static bool configured = false;
+  static PerDeviceOnce configured;      // (attributes are per device)
   int* error = nullptr;
   if (cudaGetSymbolAddress(reinterpret_cast<void**>(&error), g_error) != cudaSuccess)
     return cudaErrorInvalidValue;
-  if (!configured) {
+  if (configured.needs()) {
     cudaError_t e = cudaFuncSetAttribute(prefill_attention_kernel<D>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          Smem<D>::kBytes);
@@ -274,7 +274,7 @@ int launch(const CUtensorMap* k_map, const CUtensorMap* v_map, const __nv_bfloat
                                cudaFuncAttributePreferredSharedMemoryCarveout,
                                cudaSharedmemCarveoutMaxShared);
     if (e != cudaSuccess) return static_cast<int>(e);
-    configured = true;
+    configured.done();
   }
   const dim3 grid(n_tiles, heads);
   prefill_attention_kernel<D><<<grid, kThreads, Smem<D>::kBytes, stream>>>(

@@ -433,11 +433,11 @@ SAKV_EXPORT int sakv_prefill_attention_tc(const void* q_map, const void* k_map, 
                        (reinterpret_cast<uintptr_t>(part_o) & 15))))
     return cudaErrorInvalidValue;
   if (n_tiles == 0) return 0;
-  static bool configured = false;
+  static PerDeviceOnce configured;      // (attributes are per device)
   int* error = nullptr;
   if (cudaGetSymbolAddress(reinterpret_cast<void**>(&error), g_error) != cudaSuccess)
     return cudaErrorInvalidValue;
-  if (!configured) {
+  if (configured.needs()) {
     cudaError_t e = cudaFuncSetAttribute(prefill_attention_tc_kernel,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
     if (e == cudaSuccess)      // all of the SM's memory as shared memory: two blocks fit
@@ -445,7 +445,7 @@ SAKV_EXPORT int sakv_prefill_attention_tc(const void* q_map, const void* k_map, 
                                cudaFuncAttributePreferredSharedMemoryCarveout,
                                cudaSharedmemCarveoutMaxShared);
     if (e != cudaSuccess) return static_cast<int>(e);
-    configured = true;
+    configured.done();
   }
   prefill_attention_tc_kernel<<<dim3(heads, n_tiles), kThreads, kSmemBytes, stream>>>(
       *(const CUtensorMap*)q_map, *(const CUtensorMap*)k_map, *(const CUtensorMap*)v_map,

@@ -119,6 +119,26 @@ static inline int sm_count() {
   return known[device];
 }
 
+// A kernel's attributes (its opt-in to large dynamic shared memory) belong to a device: a
+// launcher keeps one of these per kernel and configures the kernel once on EACH device that
+// launches it. `needs()` is true until `done()` was called on the current device.
+struct PerDeviceOnce {
+  static constexpr int kDevices = 64;
+  bool set[kDevices] = {};
+  static int current() {
+    int device = 0;
+    return cudaGetDevice(&device) == cudaSuccess ? device : -1;
+  }
+  bool needs() const {
+    const int d = current();
+    return d < 0 || d >= kDevices || !set[d];
+  }
+  void done() {
+    const int d = current();
+    if (d >= 0 && d < kDevices) set[d] = true;
+  }
+};
+
 static inline int grid_for(long long work, int threads, int per_sm = 16) {
   const int cap = sm_count() * per_sm;
   long long blocks = (work + threads - 1) / threads;

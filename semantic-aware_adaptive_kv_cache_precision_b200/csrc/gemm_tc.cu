@@ -478,14 +478,14 @@ int launch(const CUtensorMap* w_map, const CUtensorMap* x_map, Params p, int n_t
            cudaStream_t stream) {
   constexpr bool kDual = kEpi == EPI_GATED;
   using C = Cfg<MT, kDual>;
-  static bool configured = false;
-  if (!configured) {
+  static PerDeviceOnce configured;      // (attributes are per device)
+  if (configured.needs()) {
     const cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<MT, kEpi>,
                                                cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                C::smem_bytes(C::kMaxStages) > 227 * 1024
                                                    ? 227 * 1024 : C::smem_bytes(C::kMaxStages));
     if (e != cudaSuccess) return static_cast<int>(e);
-    configured = true;
+    configured.done();
   }
   p.stages = C::stages_for((long long)n_tiles * m_tiles * p.splits * p.parts);
   while (C::smem_bytes(p.stages) > 227 * 1024) --p.stages;

@@ -211,12 +211,12 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constan
 __device__ int g_error;
 
 int launch(const CUtensorMap* x_map, const CUtensorMap* w_map, Params p, cudaStream_t stream) {
-  static bool configured = false;
-  if (!configured) {
+  static PerDeviceOnce configured;      // (attributes are per device)
+  if (configured.needs()) {
     const cudaError_t e = cudaFuncSetAttribute(
         gemm_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
     if (e != cudaSuccess) return static_cast<int>(e);
-    configured = true;
+    configured.done();
   }
   if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p.error), g_error) != cudaSuccess)
     return cudaErrorInvalidValue;
