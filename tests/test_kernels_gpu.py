@@ -441,6 +441,40 @@ def test_attention_decode_kernel(heads, kv_heads, d, window, splits):
     np.testing.assert_allclose(host(got), host(plain_out), rtol=0, atol=2e-2)
 
 
+@pytest.mark.parametrize("splits", [None, 1, 7, 64])
+def test_attention_decode_at_the_long_contexts_of_the_benchmark(splits):
+    """16,385 and 32,352 cached positions (block lists of more than 500 blocks, more key tiles
+    in a split than the kernel lists in shared memory) beside a short sequence."""
+    heads, kv_heads, d = 12, 2, 128
+    rng = np.random.default_rng(77)
+    lengths = [16385, 70, 32352]
+    k_cache, v_cache, table = paged_case(rng, lengths, kv_heads, d, n_blocks=768)
+    B = len(lengths)
+    qkv = dev(rng.standard_normal((B, (heads + 2 * kv_heads) * d)), torch.bfloat16)
+    scale = d ** -0.5
+    # Among thousands of random keys every output is near zero and a lost run of keys would
+    # not show: three keys of each sequence (near its start, in its middle, next to its end)
+    # are made to score 12 against the first query head of their KV head, so that they carry
+    # most of that head's weight and the crowd of the others a tenth of it.
+    group = heads // kv_heads
+    for i, n in enumerate(lengths):
+        for g in range(kv_heads):
+            query = qkv[i, g * group * d:(g * group + 1) * d].float()
+            planted = (query * (12.0 / (scale * float(query.norm()) ** 2))).to(torch.bfloat16)
+            for p_ in (5, n // 2, n - 2):
+                k_cache[int(table[i, p_ // 64]), g, p_ % 64] = planted
+    got = ops.attention_decode(qkv, k_cache, v_cache, dev(lengths, torch.int32),
+                               dev(table, torch.int32), heads, kv_heads, d, scale, None,
+                               max(lengths), splits=splits)
+    assert all(v == 0 for v in ops.kernel_errors().values())
+    q = host(qkv)[:, :heads * d].reshape(B, heads, d)
+    for i, n in enumerate(lengths):
+        kk, vv = sequence_kv(k_cache, table[i], n), sequence_kv(v_cache, table[i], n)
+        want = attention_reference(q[i], kk, vv, n - 1, heads, kv_heads, scale, None)
+        np.testing.assert_allclose(host(got[i]).reshape(heads, d), want, rtol=0, atol=1.5e-2,
+                                   err_msg=f"sequence of length {n}")
+
+
 @pytest.mark.parametrize("splits", [1, 3])
 @pytest.mark.parametrize("rotary", [False, True])
 def test_attention_decode_with_lengths_it_cannot_serve(splits, rotary):
