@@ -801,6 +801,45 @@ def test_vector_paths_of_the_elementwise_kernels(dtype):
     np.testing.assert_allclose(host(acc), want, rtol=0, atol=1e-6)
 
 
+@pytest.mark.parametrize("slots", [296, 1])
+def test_attention_prefill_tcgen05_kernel_after_a_long_prefix(slots):
+    """A chunk of a prompt after 24,576 cached positions (a query tile walks 388 key tiles:
+    the rings and their barrier phases wrap hundreds of times) beside one after 8,000, with
+    three keys of each sequence planted to carry most of its last query's weight."""
+    heads, kv_heads, d = 4, 2, 128
+    rng = np.random.default_rng(slots)
+    cases = [(24576, 200), (8000, 130)]
+    lengths = [a + n for a, n in cases]
+    k_cache, v_cache, table = paged_case(rng, lengths, kv_heads, d, n_blocks=560)
+    T = sum(n for _, n in cases)
+    qkv = dev(rng.standard_normal((T, (heads + 2 * kv_heads) * d)), torch.bfloat16)
+    scale = d ** -0.5
+    group = heads // kv_heads
+    last_rows = [cases[0][1] - 1, T - 1]
+    for i, (a, n) in enumerate(cases):
+        for g in range(kv_heads):
+            query = qkv[last_rows[i], g * group * d:(g * group + 1) * d].float()
+            planted = (query * (12.0 / (scale * float(query.norm()) ** 2))).to(torch.bfloat16)
+            for p_ in (3, a // 2 + 1, a + n - 2):
+                k_cache[int(table[i, p_ // 64]), g, p_ % 64] = planted
+    plan = ops.upload_wide_plan([a for a, _ in cases], [n for _, n in cases], heads, None, "cuda",
+                                slots=slots)
+    got = ops.attention_prefill_tc(qkv, k_cache, v_cache, *plan, dev(lengths, torch.int32),
+                                   dev(table, torch.int32), heads, kv_heads, d, scale, None)
+    assert ops.kernel_errors()["sakv_prefill_attention_tc_error"] == 0
+    q = host(qkv)[:, :heads * d].reshape(T, heads, d)
+    row = 0
+    for i, (a, n) in enumerate(cases):
+        kk = sequence_kv(k_cache, table[i], lengths[i])
+        vv = sequence_kv(v_cache, table[i], lengths[i])
+        for t in (0, 1, 63, 64, 127, 128, n - 2, n - 1):
+            want = attention_reference(q[row + t], kk, vv, a + t, heads, kv_heads, scale, None)
+            np.testing.assert_allclose(host(got[row + t]).reshape(heads, d), want, rtol=0,
+                                       atol=1.5e-2, err_msg=f"case {i}, token {t}")
+        assert np.abs(host(got[row + n - 1])).max() > 0.3        # the planted keys carry it
+        row += n
+
+
 # slots: how many blocks the plan believes run at once; 1 deals no tile to several blocks,
 # a huge number cuts every tile of more than 8 key tiles
 @pytest.mark.parametrize("heads,kv_heads,window,slots", [
