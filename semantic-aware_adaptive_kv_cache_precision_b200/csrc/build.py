@@ -45,10 +45,11 @@ LIBRARIES = {
     "attention_prefill_tc": "attention_prefill_tc.cu",
     "gemm_tc": "gemm_tc.cu",
     "gemm_wide": "gemm_wide.cu",
+    "gemm_lib": "gemm_lib.cu",
 }
 
 #: extra flags of single libraries (libraries that need the driver API, for instance)
-EXTRA_FLAGS: dict[str, list[str]] = {}
+EXTRA_FLAGS: dict[str, list[str]] = {"gemm_lib": ["-lcublas"]}
 
 
 class BuildError(RuntimeError):

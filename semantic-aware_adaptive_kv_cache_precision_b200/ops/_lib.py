@@ -39,6 +39,7 @@ SIGNATURES = {
                                   [P, P, P, P, P, I, P, I, P, P, P, P, I, I, I, I, F, I, P]),
     "sakv_gemm_tc": ("gemm_tc", [P, P, I, I, I, I, I, I, I, I, P, I, P, L, L, P]),
     "sakv_gemm_wide": ("gemm_wide", [P, P, I, I, I, I, P, L, P]),
+    "sakv_lib_accumulate": ("gemm_lib", [P, L, P, P, L, I, I, I, P, L, P]),
 }
 
 #: functions without a stream argument: (library, argument types)

@@ -25,6 +25,40 @@ from ._lib import KernelError, call, ptr, require_cuda
 TC_MAX_TOKENS = 64
 
 
+#: whether the library's products that complete an fp32 accumulator add into it themselves
+#: (cuBLAS with beta = 1, through `csrc/gemm_lib.cu`) instead of leaving the product apart
+LIBRARY_ADDS_IN_PLACE = True
+_WORKSPACE_BYTES = 64 << 20
+_workspaces: dict = {}
+
+
+_library_state = {"checked": False, "usable": False}
+
+
+def _library_adds(device) -> bool:
+    """Whether the wrapper around cuBLAS could be built and loaded here (it links against the
+    toolkit's libcublas). It is a library product like `torch.mm`: where it cannot be had,
+    the product goes through torch and a kernel of this library adds it, and a line says so."""
+    if not _library_state["checked"]:
+        _library_state["checked"] = True
+        try:
+            from ._lib import function
+            function("sakv_lib_accumulate")
+            _library_state["usable"] = True
+        except Exception as exc:              # no libcublas to link against, say
+            import sys
+            print(f"[ops] the cuBLAS wrapper is not available ({type(exc).__name__}: "
+                  f"{str(exc)[:200]}); products are added by a kernel of their own", file=sys.stderr)
+    return _library_state["usable"]
+
+
+def _library_workspace(device) -> torch.Tensor:
+    space = _workspaces.get(device)
+    if space is None:
+        space = _workspaces[device] = torch.empty(_WORKSPACE_BYTES, dtype=torch.uint8, device=device)
+    return space
+
+
 class Deferred:
     """An fp32 product that its caller still has to add to the accumulator it named."""
 
@@ -106,6 +140,12 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = No
         if out_dtype == torch.bfloat16:
             out = torch.empty((tokens, n), dtype=torch.bfloat16, device=x.device)
             return gemm_tc.gemm(xb, weight, bias, gemm_tc.EPI_BF16, out, n)
+    if accumulate_into is not None and bias is None and LIBRARY_ADDS_IN_PLACE \
+            and xb.stride(1) == 1 and acc.stride(1) == 1 and _library_adds(x.device):
+        # the library adds into the stream itself (beta = 1), as the reference's products do
+        call("sakv_lib_accumulate", ptr(xb), xb.stride(0), ptr(weight), ptr(acc), acc.stride(0),
+             tokens, n, k, ptr(_library_workspace(x.device)), _WORKSPACE_BYTES)
+        return acc
     if accumulate_into is not None:
         from . import add_into
         y = torch.mm(xb, weight.t(), out_dtype=torch.float32)

@@ -714,6 +714,30 @@ def test_gated_product_for_many_tokens(M, I, K):
     assert not gemm_wide.worth_it(64, 18944, sms=148)
 
 
+@pytest.mark.parametrize("T,N,K", [(2048, 1536, 8960), (100, 200, 136), (65, 1536, 1536), (300, 72, 64)])
+def test_library_product_adds_into_the_stream_itself(T, N, K):
+    """Above the own kernels' token count the product that completes an fp32 accumulator is
+    cuBLAS with beta = 1 (`csrc/gemm_lib.cu`): the sum against float64, on an accumulator that
+    is a view with a row stride of its own, and nothing handed back to be added later."""
+    rng = np.random.default_rng(T + N + K)
+    x = dev(rng.standard_normal((T, K)), torch.bfloat16)
+    w = dev(rng.standard_normal((N, K)) / np.sqrt(K), torch.bfloat16)
+    wide = dev(rng.standard_normal((T, N + 8)))
+    acc = wide[:, :N]
+    before, beside = host(acc), host(wide[:, N:])
+    out = ops.linear(x, w, accumulate_into=acc, may_defer=True)
+    assert out is acc
+    want = before + host(x) @ host(w).T
+    np.testing.assert_allclose(host(acc), want, rtol=0, atol=2e-5 * np.abs(want).max() + 1e-6)
+    np.testing.assert_array_equal(host(wide[:, N:]), beside)        # nothing beside it is touched
+    # with a bias the product still goes through torch and is handed back or added
+    b = dev(rng.standard_normal(N), torch.bfloat16)
+    acc2 = dev(before)
+    out = ops.linear(x, w, b, accumulate_into=acc2)
+    assert out is acc2
+    np.testing.assert_allclose(host(acc2), want + host(b), rtol=0, atol=2e-5 * np.abs(want).max() + 1e-5)
+
+
 def test_linear_hands_back_k_ranges_only_when_asked():
     rng = np.random.default_rng(5)
     x = dev(rng.standard_normal((8, 8960)), torch.bfloat16)
