@@ -1,6 +1,8 @@
 // Decode attention in bfloat16: one new token per sequence attends over its cached
 // keys and values, split along the keys (flash-decoding) so that a small batch
-// still fills the GPU, with a second kernel that folds the splits together.
+// still fills the GPU. The splits are folded together by a second kernel, or, when the
+// caller gives no scratch for partials, by the split blocks themselves as one thread-block
+// cluster, through distributed shared memory.
 //
 //   grid  = (splits, kv_heads, sequences); block = 4 warps (registers are handed out four
 //   warps at a time, so a fifth warp for the copies would halve the occupancy; lane 0 of
@@ -34,7 +36,39 @@ struct Smem {
   static constexpr int kBytes = kStages * kStageBytes + 1024 /* alignment */ + 256;
 };
 
-template <int D>
+// Largest cluster over which the splits of one (sequence, KV head) are folded inside the
+// kernel (16 needs the opt-in to non-portable cluster sizes; the launcher asks the device).
+constexpr int kMaxFoldCluster = 16;
+
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// the shared-memory address `mine` (of this block) in the block of rank `rank` of the cluster
+__device__ __forceinline__ uint32_t peer_address(uint32_t mine, int rank) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(mine), "r"(rank));
+  return remote;
+}
+__device__ __forceinline__ float peer_f32(uint32_t address) {
+  float v;
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(address) : "memory");
+  return v;
+}
+__device__ __forceinline__ float2 peer_f32x2(uint32_t address) {
+  float2 v;
+  asm volatile("ld.shared::cluster.v2.f32 {%0, %1}, [%2];"
+               : "=f"(v.x), "=f"(v.y) : "r"(address) : "memory");
+  return v;
+}
+
+// kFold: the `splits` blocks of a (sequence, KV head) are one thread-block cluster (along
+// blockIdx.x) and fold their partials themselves: each leaves its merged (maximum, sum,
+// output) per query head in its own shared memory, the cluster synchronises, and block
+// `split` finishes its share of the group's head_dim * group outputs from the peers' shared
+// memory, in the order of the splits whatever its rank. No partials in global memory and no
+// second kernel: one kernel boundary fewer in a decode step's chain.
+template <int D, bool kFold>
 __global__ void __launch_bounds__(kThreads)
 decode_attention_kernel(const __grid_constant__ CUtensorMap k_map,
                         const __grid_constant__ CUtensorMap v_map,
@@ -358,7 +392,11 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap k_map,
     }
   }
   asm volatile("bar.sync 1, %0;" ::"n"(kComputeWarps * 32));
-  if (!alive) return;
+  if (!kFold && !alive) return;
+  // (a block of a folding cluster stays for the cluster's barriers whatever happened to it;
+  // what it leaves then counts for nothing: maximum -inf, sum 0)
+  float* fold_o = sm_l + kComputeWarps * 16;                   // [group][D]   (kFold)
+  float2* fold_ml = reinterpret_cast<float2*>(fold_o + 16 * D);   // [group]
   // a warp takes query heads warp, warp + 4, ...; a lane four sizes of the head: one 16-byte
   // read per warp's share of a row, one 16-byte (bf16: 8-byte) store
 #pragma unroll 2
@@ -372,6 +410,10 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap k_map,
       weight[w] = (sm_m[w * 16 + r] == -INFINITY) ? 0.f : exp2f(sm_m[w * 16 + r] - big);
       total += weight[w] * sm_l[w * 16 + r];
     }
+    if (kFold && !alive) {
+      big = -INFINITY;
+      total = 0.f;
+    }
     const int h = g * group + r;
     if (lane < D / 4) {
       float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -381,7 +423,10 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap k_map,
         acc.x += weight[w] * v.x; acc.y += weight[w] * v.y;
         acc.z += weight[w] * v.z; acc.w += weight[w] * v.w;
       }
-      if (splits == 1) {
+      if (kFold) {
+        if (!alive) acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        *reinterpret_cast<float4*>(fold_o + r * D + lane * 4) = acc;
+      } else if (splits == 1) {
         const float inv = total > 0.f ? 1.f / total : 0.f;      // no key at all: zeros
         *reinterpret_cast<uint2*>(out + ((long long)b * heads + h) * D + lane * 4) =
             make_uint2(mma::pack_bf16(acc.x * inv, acc.y * inv),
@@ -391,11 +436,57 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap k_map,
                                    lane * 4) = acc;
       }
     }
-    if (splits > 1 && lane == 0) {
+    if (kFold) {
+      if (lane == 0) fold_ml[r] = make_float2(big, total);
+    } else if (splits > 1 && lane == 0) {
       float* ml = part_ml + (((long long)b * heads + h) * splits + split) * 2;
       ml[0] = big;
       ml[1] = total;
     }
+  }
+  if (kFold) {
+    cluster_sync_all();          // every block's (maximum, sum, output) lies in its shared memory
+    // The group's outputs are one row of group * D elements (head r, size), dealt to the
+    // blocks in equal runs. A thread takes one element of its block's run at a time and
+    // reads the splits' maxima, sums and outputs eight at a time, all loads of a round in
+    // flight together; rounds are merged like tiles of an online softmax, in order.
+    const int elements = group * D;
+    const int run = (elements + splits - 1) / splits;
+    const int e_end = min(elements, (split + 1) * run);
+    constexpr int kRound = 8;
+    for (int e = split * run + threadIdx.x; e < e_end; e += kThreads) {
+      const int r = e / D;
+      const uint32_t ml_at = tma::smem_u32(fold_ml + r), o_at = tma::smem_u32(fold_o + e);
+      float big = -INFINITY, total = 0.f, acc = 0.f;
+      for (int s0 = 0; s0 < splits; s0 += kRound) {
+        float2 v[kRound];
+        float o_s[kRound];
+#pragma unroll
+        for (int j = 0; j < kRound; ++j) {
+          const bool live = s0 + j < splits;
+          const int rank = live ? s0 + j : 0;
+          v[j] = live ? peer_f32x2(peer_address(ml_at, rank)) : make_float2(-INFINITY, 0.f);
+          o_s[j] = live ? peer_f32(peer_address(o_at, rank)) : 0.f;
+        }
+        float round_max = big;
+#pragma unroll
+        for (int j = 0; j < kRound; ++j) round_max = fmaxf(round_max, v[j].x);
+        if (round_max == -INFINITY) continue;
+        const float keep = exp2f(big - round_max);          // 0 the first time
+        total *= keep;
+        acc *= keep;
+        big = round_max;
+#pragma unroll
+        for (int j = 0; j < kRound; ++j) {
+          const float w = exp2f(v[j].x - big);              // 0 for a split that saw no key
+          total += w * v[j].y;
+          acc += w * o_s[j];
+        }
+      }
+      out[((long long)b * heads + g * group) * D + e] =
+          __float2bfloat16_rn(total > 0.f ? acc / total : 0.f);
+    }
+    cluster_sync_all();          // nobody leaves while a peer may still read its shared memory
   }
 }
 
@@ -501,6 +592,46 @@ __global__ void combine_groups_kernel(const float* __restrict__ part_o, const fl
 
 __device__ int g_error;
 
+// The largest cluster the folding kernel can be launched with on this device: 16 where the
+// opt-in to non-portable sizes is granted and such a cluster fits, else 8 (0: none).
+template <int D>
+int max_fold_cluster() {
+  static int known[64] = {};
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return 0;
+  if (known[device]) return known[device] - 1;
+  auto kernel = decode_attention_kernel<D, true>;
+  int best = 0;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem<D>::kBytes) ==
+      cudaSuccess) {
+    const bool wide = cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed,
+                                           1) == cudaSuccess;
+    for (int size : {16, 8}) {
+      if (size > 8 && !wide) continue;
+      cudaLaunchConfig_t config = {};
+      config.gridDim = dim3(size, 1, 1);
+      config.blockDim = dim3(kThreads);
+      config.dynamicSmemBytes = Smem<D>::kBytes;
+      cudaLaunchAttribute attr[1];
+      attr[0].id = cudaLaunchAttributeClusterDimension;
+      attr[0].val.clusterDim.x = size;
+      attr[0].val.clusterDim.y = 1;
+      attr[0].val.clusterDim.z = 1;
+      config.attrs = attr;
+      config.numAttrs = 1;
+      int clusters = 0;
+      if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &config) == cudaSuccess && clusters > 0) {
+        best = size;
+        break;
+      }
+    }
+    cudaGetLastError();      // (a refused size is an answer, not an error to keep)
+  }
+  known[device] = best + 1;
+  return best;
+}
+
+// `part_o == nullptr` with more than one split: the splits fold themselves as a cluster.
 template <int D>
 int launch(const CUtensorMap* k_map, const CUtensorMap* v_map, const __nv_bfloat16* q,
            long long q_stride, const int32_t* seq_lens, const int32_t* block_table, int max_blocks,
@@ -513,22 +644,34 @@ int launch(const CUtensorMap* k_map, const CUtensorMap* v_map, const __nv_bfloat
   if (cudaGetSymbolAddress(reinterpret_cast<void**>(&error), g_error) != cudaSuccess)
     return cudaErrorInvalidValue;
   if (configured.needs()) {
-    cudaError_t e = cudaFuncSetAttribute(decode_attention_kernel<D>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         Smem<D>::kBytes);
-    if (e == cudaSuccess)      // all of the SM's memory as shared memory: two blocks fit
-      e = cudaFuncSetAttribute(decode_attention_kernel<D>,
-                               cudaFuncAttributePreferredSharedMemoryCarveout,
-                               cudaSharedmemCarveoutMaxShared);
+    cudaError_t e = cudaSuccess;
+    for (int fold = 0; fold < 2 && e == cudaSuccess; ++fold) {
+      const void* kernel = fold ? (const void*)decode_attention_kernel<D, true>
+                                : (const void*)decode_attention_kernel<D, false>;
+      e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               Smem<D>::kBytes);
+      if (e == cudaSuccess)      // all of the SM's memory as shared memory: two blocks fit
+        e = cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                 cudaSharedmemCarveoutMaxShared);
+    }
     if (e != cudaSuccess) return static_cast<int>(e);
     configured.done();
   }
   const dim3 grid(splits, kv_heads, sequences);
-  int status = launch_overlapped(decode_attention_kernel<D>, grid, dim3(kThreads), Smem<D>::kBytes,
-                                 stream, 1, *k_map, *v_map, q, q_stride, seq_lens, block_table,
-                                 max_blocks, out, part_o, part_ml, heads, kv_heads, splits,
-                                 scale * 1.4426950408889634f, window, error, cos_t,
-                                 sin_t, rotary_rows, k_out, v_out);
+  if (splits > 1 && part_o == nullptr) {
+    if (splits > max_fold_cluster<D>()) return cudaErrorInvalidValue;
+    return launch_overlapped_cluster(decode_attention_kernel<D, true>, grid, dim3(kThreads),
+                                     Smem<D>::kBytes, stream, dim3(splits, 1, 1), *k_map, *v_map,
+                                     q, q_stride, seq_lens, block_table, max_blocks, out, part_o,
+                                     part_ml, heads, kv_heads, splits,
+                                     scale * 1.4426950408889634f, window, error, cos_t, sin_t,
+                                     rotary_rows, k_out, v_out);
+  }
+  int status = launch_overlapped(decode_attention_kernel<D, false>, grid, dim3(kThreads),
+                                 Smem<D>::kBytes, stream, 1, *k_map, *v_map, q, q_stride,
+                                 seq_lens, block_table, max_blocks, out, part_o, part_ml, heads,
+                                 kv_heads, splits, scale * 1.4426950408889634f, window, error,
+                                 cos_t, sin_t, rotary_rows, k_out, v_out);
   const int fold_groups = min(kFoldGroups, (splits + 15) / 16);
   if (status == 0 && splits > 1 && fold_groups == 1)
     status = launch_overlapped(combine_kernel, dim3(sequences * heads), dim3(D <= 128 ? D : 128),
@@ -572,7 +715,8 @@ SAKV_EXPORT int sakv_decode_attention(const void* k_map, const void* v_map, cons
       (cos_table && (((uintptr_t)q & 15) || (q_stride & 7))))
     return cudaErrorInvalidValue;
   if (sequences < 0 || heads <= 0 || kv_heads <= 0 || heads % kv_heads || heads / kv_heads > 16 ||
-      splits < 1 || max_blocks <= 0 || (splits > 1 && (!part_o || !part_ml || (reinterpret_cast<uintptr_t>(part_ml) & 7))))
+      splits < 1 || max_blocks <= 0 || (part_o == nullptr) != (part_ml == nullptr) ||
+      (reinterpret_cast<uintptr_t>(part_ml) & 7))
     return cudaErrorInvalidValue;
   if (sequences == 0) return 0;
   if (sequences > 65535 || kv_heads > 65535) return cudaErrorInvalidValue;
@@ -586,6 +730,14 @@ SAKV_EXPORT int sakv_decode_attention(const void* k_map, const void* v_map, cons
   if (head_dim == 128) GO(128);
 #undef GO
   return cudaErrorInvalidValue;
+}
+
+// How many splits the kernel can fold by itself, as one thread-block cluster (16 or 8; 0 if
+// the head size is not served). More splits need `part_o`, `part_ml` and the fold kernel.
+SAKV_EXPORT int sakv_decode_attention_max_cluster(int head_dim) {
+  if (head_dim == 64) return max_fold_cluster<64>();
+  if (head_dim == 128) return max_fold_cluster<128>();
+  return 0;
 }
 
 // The error word that a timed-out wait leaves (0 = none); reading it synchronises.

@@ -72,10 +72,11 @@ __device__ __forceinline__ void let_next_kernel_start() {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
 
+// `cluster`: the thread-block cluster's shape, (1, 1, 1) for none.
 template <typename... KernelArgs, typename... Args>
-static inline int launch_overlapped(void (*kernel)(KernelArgs...), dim3 grid, dim3 block,
-                                    size_t smem, cudaStream_t stream, int cluster_z,
-                                    Args&&... args) {
+static inline int launch_overlapped_cluster(void (*kernel)(KernelArgs...), dim3 grid, dim3 block,
+                                            size_t smem, cudaStream_t stream, dim3 cluster,
+                                            Args&&... args) {
   cudaLaunchConfig_t config = {};
   config.gridDim = grid;
   config.blockDim = block;
@@ -86,11 +87,11 @@ static inline int launch_overlapped(void (*kernel)(KernelArgs...), dim3 grid, di
   attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[n].val.programmaticStreamSerializationAllowed = 1;
   ++n;
-  if (cluster_z > 1) {
+  if (cluster.x * cluster.y * cluster.z > 1) {
     attr[n].id = cudaLaunchAttributeClusterDimension;
-    attr[n].val.clusterDim.x = 1;
-    attr[n].val.clusterDim.y = 1;
-    attr[n].val.clusterDim.z = cluster_z;
+    attr[n].val.clusterDim.x = cluster.x;
+    attr[n].val.clusterDim.y = cluster.y;
+    attr[n].val.clusterDim.z = cluster.z;
     ++n;
     // (the blocks of a cluster are there to pull weights through as many SMs as possible)
     attr[n].id = cudaLaunchAttributeClusterSchedulingPolicyPreference;
@@ -101,6 +102,15 @@ static inline int launch_overlapped(void (*kernel)(KernelArgs...), dim3 grid, di
   config.numAttrs = n;
   const cudaError_t e = cudaLaunchKernelEx(&config, kernel, static_cast<KernelArgs>(args)...);
   return e != cudaSuccess ? static_cast<int>(e) : launch_status();
+}
+
+template <typename... KernelArgs, typename... Args>
+static inline int launch_overlapped(void (*kernel)(KernelArgs...), dim3 grid, dim3 block,
+                                    size_t smem, cudaStream_t stream, int cluster_z,
+                                    Args&&... args) {
+  return launch_overlapped_cluster(kernel, grid, block, smem, stream,
+                                   dim3(1, 1, cluster_z > 1 ? cluster_z : 1),
+                                   static_cast<Args&&>(args)...);
 }
 
 // The number of SMs of the current device, asked once per device (148 on a B200; fewer on

@@ -47,6 +47,7 @@ PLAIN_SIGNATURES = {
     "sakv_choose_chunks": ("sampling", [I]),
     "sakv_decode_attention_map": ("attention_decode", [P, P, L, I, I]),
     "sakv_decode_attention_error": ("attention_decode", [P]),
+    "sakv_decode_attention_max_cluster": ("attention_decode", [I]),
     "sakv_prefill_attention_error": ("attention_prefill", [P]),
     "sakv_prefill_attention_tc_error": ("attention_prefill_tc", [P]),
     "sakv_prefill_attention_tc_qmap": ("attention_prefill_tc", [P, P, L, L, L]),

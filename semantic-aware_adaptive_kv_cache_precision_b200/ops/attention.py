@@ -40,6 +40,26 @@ def tensor_map(cache: torch.Tensor):
     return hit[1]
 
 
+# The numbers of splits whose blocks fold their partials themselves, as one thread-block
+# cluster, instead of leaving them to a second kernel. Measured inside the decode step at the
+# 1.5B widths, 2,048 cached tokens (ms a step, second kernel / cluster): 64 sequences (2
+# splits) 2.09 / 2.06, 32 (4) 1.59 / 1.53; but 48 (3) 1.86 / 2.10, 24 (6) 1.47 / 1.58, 16 (9)
+# 1.34 / 1.47, 12 (11) 1.31 / 1.45, 8 (9) 1.216 / 1.218, 8 (8) 1.222, 4 (16) 1.20 against 1.15
+# with 18 splits: clusters of 2 and 4 find their SMs at once, the others wait for a placement.
+FOLD_IN_CLUSTER = (2, 4)
+
+_fold_limit: dict = {}
+
+
+def fold_cluster_limit(head_dim: int) -> int:
+    """How many splits the decode kernel folds by itself, as one thread-block cluster (asked of
+    the device once: 16 where non-portable cluster sizes are granted, else 8)."""
+    key = (head_dim, torch.cuda.current_device())
+    if key not in _fold_limit:
+        _fold_limit[key] = int(plain_function("sakv_decode_attention_max_cluster")(head_dim))
+    return _fold_limit[key]
+
+
 def decode_splits(sequences: int, kv_heads: int, max_len: int, sms: int | None = None) -> int:
     """How many ways to split the keys. Either one block per SM, however short its run of
     keys, or, when that leaves runs of many tiles, two blocks per SM with at least three
@@ -59,7 +79,8 @@ def decode_splits(sequences: int, kv_heads: int, max_len: int, sms: int | None =
 def attention_decode(qkv: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                      seq_lens: torch.Tensor, block_table: torch.Tensor, heads: int, kv_heads: int,
                      head_dim: int, scale: float, window, max_len: int,
-                     splits: int | None = None, rotary=None, write_cache: bool = True) -> torch.Tensor:
+                     splits: int | None = None, rotary=None, write_cache: bool = True,
+                     in_cluster: bool | None = None) -> torch.Tensor:
     """One query token per sequence (row b of `qkv` belongs to sequence b).
 
     `rotary`: None, or `(cos, sin)` (fp32 [positions, head_dim / 2], rotation over the whole
@@ -76,9 +97,16 @@ def attention_decode(qkv: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Te
         raise KernelError("attention_decode: one length and one block list per sequence")
     if splits is None:
         splits = decode_splits(sequences, kv_heads, max_len)
+    if in_cluster is None:
+        in_cluster = splits in FOLD_IN_CLUSTER
+    if in_cluster and not 1 < splits <= fold_cluster_limit(head_dim):
+        if splits > 1:
+            raise KernelError(f"attention_decode: {splits} splits do not fold as one cluster "
+                              f"(at most {fold_cluster_limit(head_dim)})")
+        in_cluster = False
     out = torch.empty((sequences, heads * head_dim), dtype=torch.bfloat16, device=qkv.device)
     part_o = part_ml = None
-    if splits > 1:
+    if splits > 1 and not in_cluster:
         part_o = torch.empty((sequences, heads, splits, head_dim), dtype=torch.float32,
                              device=qkv.device)
         part_ml = torch.empty((sequences, heads, splits, 2), dtype=torch.float32,
@@ -88,7 +116,7 @@ def attention_decode(qkv: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Te
          ptr(part_o), ptr(part_ml), sequences, heads, kv_heads, head_dim, splits, float(scale),
          int(window) if window else 0, *_rotary_arguments(rotary, write_cache, qkv, k_cache, v_cache,
                                                          heads, kv_heads, head_dim, max_len))
-    if splits > 1:
+    if part_o is not None:
         _lib.launches += 1          # the call launched the fold kernel too
     return out
 

@@ -441,6 +441,62 @@ def test_attention_decode_kernel(heads, kv_heads, d, window, splits):
     np.testing.assert_allclose(host(got), host(plain_out), rtol=0, atol=2e-2)
 
 
+@pytest.mark.parametrize("heads,kv_heads,d,window", [(12, 2, 128, None), (4, 4, 64, None),
+                                                     (16, 1, 128, None), (6, 3, 64, 100),
+                                                     (14, 2, 128, 64)])
+@pytest.mark.parametrize("splits", [2, 3, 4, 7, 8, 16])
+@pytest.mark.parametrize("rotary", [False, True])
+def test_attention_decode_folds_its_splits_as_a_cluster(heads, kv_heads, d, window, splits, rotary):
+    """The splits of a (sequence, KV head) as one thread-block cluster that folds its partials
+    through distributed shared memory (what the step uses for 2 and 4 splits): the float64
+    reference's output, the second-kernel path's to a rounding of the fold's sums, the same
+    cache afterwards; sequences with fewer key tiles than splits (blocks with no key) and
+    lengths the kernel cannot serve among them."""
+    rng = np.random.default_rng(heads * d + (window or 0) + splits)
+    lengths = [1, 63, 64, 65, 700, 2048, 129, 0]
+    k_cache, v_cache, table = paged_case(rng, [max(n, 1) for n in lengths], kv_heads, d)
+    if window:
+        for i, n in enumerate(lengths):
+            table[i, :max(0, n - window) // 64] = -1
+    B = len(lengths)
+    qkv = dev(rng.standard_normal((B, (heads + 2 * kv_heads) * d)), torch.bfloat16)
+    j = np.arange(d // 2)
+    angle = np.arange(2304)[:, None] * np.power(1e4, -2.0 * j / d)[None, :]
+    tables = (dev(np.cos(angle)), dev(np.sin(angle))) if rotary else None
+    lens, tab = dev(lengths, torch.int32), dev(table, torch.int32)
+    scale = d ** -0.5
+    assert splits <= ops.attention.fold_cluster_limit(d)
+    caches = [(k_cache.clone(), v_cache.clone()) for _ in range(2)]
+    got, want = (ops.attention_decode(qkv, kc, vc, lens, tab, heads, kv_heads, d, scale, window,
+                                      max(lengths), splits=splits, rotary=tables, in_cluster=way)
+                 for way, (kc, vc) in zip((True, False), caches))
+    assert all(v == 0 for v in ops.kernel_errors().values())
+    assert torch.isfinite(got.float()).all() and torch.count_nonzero(got[-1]) == 0
+    np.testing.assert_allclose(host(got), host(want), rtol=0, atol=2.0 ** -7)
+    for a, b in zip(caches[0], caches[1]):
+        np.testing.assert_array_equal(host(a), host(b))          # (NaN in unused blocks)
+    if not rotary:
+        q = host(qkv)[:, :heads * d].reshape(B, heads, d)
+        for i, n in enumerate(lengths[:-1]):
+            first = max(0, n - window) if window else 0
+            kk, vv = np.zeros((n, kv_heads, d)), np.zeros((n, kv_heads, d))
+            kc, vc = host(k_cache), host(v_cache)
+            for p_ in range(first, n):
+                kk[p_], vv[p_] = kc[table[i, p_ // 64], :, p_ % 64], vc[table[i, p_ // 64], :, p_ % 64]
+            ref = attention_reference(q[i], kk, vv, n - 1, heads, kv_heads, scale, window)
+            np.testing.assert_allclose(host(got[i]).reshape(heads, d), ref, rtol=0, atol=1.5e-2,
+                                       err_msg=f"sequence {i} of length {n}")
+
+
+def test_attention_decode_refuses_a_cluster_it_cannot_launch():
+    rng = np.random.default_rng(3)
+    k_cache, v_cache, table = paged_case(rng, [200], 1, 64)
+    qkv = dev(rng.standard_normal((1, 4 * 64)), torch.bfloat16)
+    with pytest.raises(ops.KernelError, match="do not fold as one cluster"):
+        ops.attention_decode(qkv, k_cache, v_cache, dev([200], torch.int32), dev(table, torch.int32),
+                             2, 1, 64, 0.125, None, 200, splits=17, in_cluster=True)
+
+
 @pytest.mark.parametrize("splits", [None, 1, 7, 64])
 def test_attention_decode_at_the_long_contexts_of_the_benchmark(splits):
     """16,385 and 32,352 cached positions (block lists of more than 500 blocks, more key tiles
