@@ -45,6 +45,7 @@ LIBRARIES = {
     "attention_prefill_tc": "attention_prefill_tc.cu",
     "gemm_tc": "gemm_tc.cu",
     "gemm_wide": "gemm_wide.cu",
+    "gemm_pair": "gemm_pair.cu",
     "gemm_lib": "gemm_lib.cu",
 }
 

@@ -140,4 +140,43 @@ __device__ __forceinline__ void st_32x32b_x32(uint32_t taddr, const uint32_t (&v
   asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 
+// ---- two blocks of a cluster (on the two SMs of a pair) working on one product --------------
+// `cta_group::2`: the MMA's 256 rows are 128 of each block (each block's tensor memory holds
+// its own 128 rows of the accumulator), each block supplies half of B's rows from its own
+// shared memory at the same offsets, and ONE thread of the pair's first block issues.
+
+// The same warp of BOTH blocks allocates; `dst` is the same shared-memory offset in both.
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* dst, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                   static_cast<uint32_t>(__cvta_generic_to_shared(dst))),
+               "r"(cols)
+               : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols)
+               : "memory");
+}
+
+__device__ __forceinline__ void mma_ss_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                            uint32_t idesc, bool accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(static_cast<uint32_t>(accumulate))
+      : "memory");
+}
+
+// The mbarrier at this shared-memory offset in EACH block of `mask` (bit = rank in the
+// cluster) gets one arrival when every MMA issued so far by this thread is done.
+__device__ __forceinline__ void commit_pair(uint64_t* bar, uint16_t mask) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 "
+      "[%0], %1;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(bar))),
+      "h"(mask)
+      : "memory");
+}
+
 }  // namespace tc

@@ -39,6 +39,7 @@ SIGNATURES = {
                                   [P, P, P, P, P, I, P, I, P, P, P, P, I, I, I, I, F, I, P]),
     "sakv_gemm_tc": ("gemm_tc", [P, P, I, I, I, I, I, I, I, I, P, I, P, L, L, P]),
     "sakv_gemm_wide": ("gemm_wide", [P, P, I, I, I, I, P, L, P]),
+    "sakv_gemm_pair": ("gemm_pair", [P, P, I, I, I, I, P, L, P]),
     "sakv_lib_accumulate": ("gemm_lib", [P, L, P, P, L, I, I, I, P, L, P]),
 }
 
@@ -54,6 +55,8 @@ PLAIN_SIGNATURES = {
     "sakv_gemm_tc_map": ("gemm_tc", [P, P, L, L, L, I]),
     "sakv_gemm_wide_map": ("gemm_wide", [P, P, L, L, L]),
     "sakv_gemm_wide_error": ("gemm_wide", [P]),
+    "sakv_gemm_pair_error": ("gemm_pair", [P]),
+    "sakv_gemm_pair_resident": ("gemm_pair", []),
     "sakv_gemm_tc_splits": ("gemm_tc", [I, I]),
     "sakv_gemm_tc_max_clusters": ("gemm_tc", [I, I, I]),
     "sakv_gemm_tc_error": ("gemm_tc", [P]),

@@ -29,6 +29,30 @@ def worth_it(tokens: int, inter: int, sms: int | None = None) -> bool:
     return tokens > 64 and tiles >= 0.85 * waves * sms and tokens >= 0.8 * token_tiles * TILE_TOKENS
 
 
+def pair_worth_it(tokens: int) -> bool:
+    """Whether the kernel on pairs of SMs beats the library's product followed by the
+    activation kernel: where its token tiles of 256 are well filled, or there is only one.
+    Measured with cold weights, pair / single block / library (us): 1536 -> 2 x 8960: 128
+    tokens 21.0 / 27.4 / 34.6, 256: 20.4 / 29.2 / 35.1, 512: 27.5 / 29.2 / 36.5, 768: 35.9 /
+    47.4 / 41.6, 1,024: 44.0 / 46.9 / 51.5, 2,048: 81.7 / 87.1 / 95.2, 8,192: 298 / 337 / 438;
+    3584 -> 2 x 18944: 128: 56 / 59 / 61, 256: 58 / 60 / 79, 384: 95 / 98 / 85 (token tiles
+    three quarters full), 512: 100 / 101 / 103, 1,024: 184 / 192 / 202, 2,048: 377 / 416 / 453;
+    5120 -> 2 x 27648: 128: 116 / 156 / 116, 384: 207 / 219 / 176, 2,048: 809 / 870 / 900."""
+    token_tiles = -(-tokens // TILE_TOKENS)
+    return tokens > 64 and (token_tiles == 1 or tokens >= 0.8 * token_tiles * TILE_TOKENS)
+
+
+_pairs: dict = {}
+
+
+def resident_pairs() -> int:
+    """Pairs of SMs that hold the pair kernel at one time (74 on a B200; 0: not here)."""
+    device = torch.cuda.current_device()
+    if device not in _pairs:
+        _pairs[device] = int(plain_function("sakv_gemm_pair_resident")())
+    return _pairs[device]
+
+
 _weight_maps: dict = {}
 
 
@@ -69,6 +93,24 @@ def gated(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
     call("sakv_gemm_wide", x_map, _weight_map(w_gate_up), x.shape[0], inter, x.shape[1], inter,
          ptr(out), out.stride(0))
     return out
+
+
+def gated_pair(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
+    """The same product on pairs of SMs (`csrc/gemm_pair.cu`, tcgen05 with `cta_group::2`)."""
+    inter = w_gate_up.shape[0] // 2
+    if inter % 8:
+        raise KernelError("gemm_wide.gated_pair: the intermediate size must be a multiple of 8")
+    out = torch.empty((x.shape[0], inter), dtype=torch.bfloat16, device=x.device)
+    x_raw, x_map = _make_map(x)
+    call("sakv_gemm_pair", x_map, _weight_map(w_gate_up), x.shape[0], inter, x.shape[1], inter,
+         ptr(out), out.stride(0))
+    return out
+
+
+def pair_error_word() -> int:
+    value = ctypes.c_int(0)
+    code = plain_function("sakv_gemm_pair_error")(ctypes.addressof(value))
+    return value.value if code == 0 else -code
 
 
 def error_word() -> int:

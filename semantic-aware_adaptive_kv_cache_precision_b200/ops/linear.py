@@ -77,8 +77,11 @@ def gated_up(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
     if x.shape[0] <= TC_MAX_TOKENS and inter % 128 == 0 and gemm_tc.takes(x, w_gate_up):
         out = torch.empty((x.shape[0], inter), dtype=torch.bfloat16, device=x.device)
         return gemm_tc.gemm(x, w_gate_up, None, gemm_tc.EPI_GATED, out, inter, dual_offset=inter)
-    if gemm_wide.worth_it(x.shape[0], inter) and inter % 8 == 0 and gemm_wide.takes(x, w_gate_up):
-        return gemm_wide.gated(x, w_gate_up)
+    if inter % 8 == 0 and gemm_wide.takes(x, w_gate_up):
+        if gemm_wide.pair_worth_it(x.shape[0]) and gemm_wide.resident_pairs() > 0:
+            return gemm_wide.gated_pair(x, w_gate_up)
+        if gemm_wide.worth_it(x.shape[0], inter):
+            return gemm_wide.gated(x, w_gate_up)
     return gated_silu(linear(x, w_gate_up, out_dtype=x.dtype))
 
 

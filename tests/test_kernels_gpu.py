@@ -742,26 +742,45 @@ def test_gemm_tc_k_ranges_summed_apart(M, N, K, parts, splits):
     assert torch.equal(stream, apart) and torch.equal(got_normed, want_normed)
 
 
+@pytest.mark.parametrize("kernel", ["pair", "single"])
 @pytest.mark.parametrize("M,I,K", [(1030, 384, 1536), (256, 200, 72), (2048, 8960, 1536),
-                                   (700, 128, 64), (513, 1096, 328)])
-def test_gated_product_for_many_tokens(M, I, K):
-    """The tcgen05 product with the gated SiLU in its epilogue against float64, and against
-    the library's product followed by the activation kernel (a bf16 rounding apart)."""
+                                   (700, 128, 64), (513, 1096, 328), (65, 8, 8), (300, 18944, 136),
+                                   (4200, 264, 3000)])
+def test_gated_product_for_many_tokens(M, I, K, kernel):
+    """The tcgen05 products with the gated SiLU in their epilogue (on pairs of SMs with
+    `cta_group::2`, and on single blocks) against float64, and against the library's product
+    followed by the activation kernel (a bf16 rounding apart): token counts that fill no
+    tile, more tiles than pairs (several rounds through both accumulators), a K of one step and
+    of 47, intermediate sizes that fill no tile of weight rows."""
     from semantic_aware_adaptive_kv_cache_precision_b200.ops import gemm_wide
     rng = np.random.default_rng(M + I + K)
     x = dev(rng.standard_normal((M, K)), torch.bfloat16)
     w = dev(rng.standard_normal((2 * I, K)) * (2.0 / np.sqrt(K)), torch.bfloat16)
     assert gemm_wide.takes(x, w)
-    got = host(gemm_wide.gated(x, w))
-    assert gemm_wide.error_word() == 0
+    if kernel == "pair":
+        assert gemm_wide.resident_pairs() > 0
+        run, word = gemm_wide.gated_pair, gemm_wide.pair_error_word
+    else:
+        run, word = gemm_wide.gated, gemm_wide.error_word
+    got = host(run(x, w))
+    assert word() == 0
     both = host(x) @ host(w).T
     gate, up = both[:, :I], both[:, I:]
     want = gate / (1 + np.exp(-gate)) * up
     assert np.abs(got - want).max() <= 2.0 ** -8 * (np.abs(want).max() + 1) * 1.5
     twin = host(ops.gated_silu(torch.mm(x, w.t())))
     assert np.abs(got - twin).max() <= 2.0 ** -7 * (np.abs(want).max() + 1)
-    if gemm_wide.worth_it(M, I):
-        assert torch.equal(ops.gated_up(x, w), gemm_wide.gated(x, w))    # the product path takes it
+    assert torch.equal(run(x, w), run(x, w))                 # (the same sums every time)
+    if kernel == "pair" and gemm_wide.pair_worth_it(M):
+        assert torch.equal(ops.gated_up(x, w), gemm_wide.gated_pair(x, w))    # the product path takes it
+
+
+def test_which_gated_product_runs():
+    from semantic_aware_adaptive_kv_cache_precision_b200.ops import gemm_wide
+    # on pairs: one token tile, or token tiles at least four fifths full
+    assert all(gemm_wide.pair_worth_it(t) for t in (65, 128, 256, 410, 512, 768, 1024, 2048, 8192))
+    assert not any(gemm_wide.pair_worth_it(t) for t in (1, 64, 257, 384, 600))
+    # single blocks (where no pair can be placed): whole waves of tiles, full token tiles
     assert gemm_wide.worth_it(2048, 8960, sms=148) and gemm_wide.worth_it(512, 8960, sms=148)
     assert gemm_wide.worth_it(256, 18944, sms=148)              # 148 tiles: one full wave
     assert not gemm_wide.worth_it(256, 8960, sms=148)           # 70 tiles: half a wave
