@@ -31,15 +31,20 @@ def worth_it(tokens: int, inter: int, sms: int | None = None) -> bool:
 
 def pair_worth_it(tokens: int) -> bool:
     """Whether the kernel on pairs of SMs beats the library's product followed by the
-    activation kernel: where its token tiles of 256 are well filled, or there is only one.
+    activation kernel: where its token tiles of 256 are at least five eighths (one tile) or
+    four fifths (several) full.
     Measured with cold weights, pair / single block / library (us): 1536 -> 2 x 8960: 128
     tokens 21.0 / 27.4 / 34.6, 256: 20.4 / 29.2 / 35.1, 512: 27.5 / 29.2 / 36.5, 768: 35.9 /
     47.4 / 41.6, 1,024: 44.0 / 46.9 / 51.5, 2,048: 81.7 / 87.1 / 95.2, 8,192: 298 / 337 / 438;
     3584 -> 2 x 18944: 128: 56 / 59 / 61, 256: 58 / 60 / 79, 384: 95 / 98 / 85 (token tiles
     three quarters full), 512: 100 / 101 / 103, 1,024: 184 / 192 / 202, 2,048: 377 / 416 / 453;
-    5120 -> 2 x 27648: 128: 116 / 156 / 116, 384: 207 / 219 / 176, 2,048: 809 / 870 / 900."""
+    5120 -> 2 x 27648: 128: 116 / 156 / 116, 384: 207 / 219 / 176, 2,048: 809 / 870 / 900.
+    Inside a decode step at the 1.5B widths, whose weights come from memory every time (ms a
+    step, pair / library): 96 sequences 2.505 / 2.461, 128: 2.759 / 2.740, 192: 3.885 / 3.937,
+    256: 4.093 / 4.148."""
     token_tiles = -(-tokens // TILE_TOKENS)
-    return tokens > 64 and (token_tiles == 1 or tokens >= 0.8 * token_tiles * TILE_TOKENS)
+    fill = tokens / (token_tiles * TILE_TOKENS)
+    return fill >= (0.625 if token_tiles == 1 else 0.8)
 
 
 _pairs: dict = {}

@@ -777,9 +777,9 @@ def test_gated_product_for_many_tokens(M, I, K, kernel):
 
 def test_which_gated_product_runs():
     from semantic_aware_adaptive_kv_cache_precision_b200.ops import gemm_wide
-    # on pairs: one token tile, or token tiles at least four fifths full
-    assert all(gemm_wide.pair_worth_it(t) for t in (65, 128, 256, 410, 512, 768, 1024, 2048, 8192))
-    assert not any(gemm_wide.pair_worth_it(t) for t in (1, 64, 257, 384, 600))
+    # on pairs: token tiles at least five eighths (one tile) or four fifths (several) full
+    assert all(gemm_wide.pair_worth_it(t) for t in (160, 256, 410, 512, 768, 1024, 2048, 8192))
+    assert not any(gemm_wide.pair_worth_it(t) for t in (1, 64, 65, 128, 159, 257, 384, 600))
     # single blocks (where no pair can be placed): whole waves of tiles, full token tiles
     assert gemm_wide.worth_it(2048, 8960, sms=148) and gemm_wide.worth_it(512, 8960, sms=148)
     assert gemm_wide.worth_it(256, 18944, sms=148)              # 148 tiles: one full wave
