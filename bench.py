@@ -300,10 +300,13 @@ def kernel_case(name: str) -> int:
     def weights(n, k, copies):
         return [torch.randn(n, k, device=dev, dtype=torch.bfloat16) * 0.02 for _ in range(copies)]
 
-    if name == "gemm_gated_2048":
+    if name in ("gemm_gated_2048", "gemm_gated_single_2048"):
+        # the feed-forward's gated product as the prefill step runs it (pairs of SMs), or the
+        # single-block kernel that stands in where no pair can be placed
         from semantic_aware_adaptive_kv_cache_precision_b200.ops import gemm_wide
         ws, x = weights(2 * I, H, 3), torch.randn(PREFILL_TOKENS, H, device=dev, dtype=torch.bfloat16)
-        run = lambda i: gemm_wide.gated(x, ws[i % 3])
+        fn = ops.gated_up if name == "gemm_gated_2048" else gemm_wide.gated
+        run = lambda i: fn(x, ws[i % 3])
     elif name.startswith("gemm_"):
         _, which, batch = name.split("_", 2)
         m = int(batch.lstrip("b"))
