@@ -262,9 +262,18 @@ int resident_pairs() {
 // cannot run here).
 SAKV_EXPORT int sakv_gemm_pair_resident() { return resident_pairs(); }
 
+// A TMA descriptor of a row-major bf16 matrix [rows, cols] read in boxes of [128 rows, 64
+// columns]; `map` points to 128 bytes on the host.
+SAKV_EXPORT int sakv_gemm_pair_map(void* map, const void* base, long long rows, long long cols,
+                                   long long row_stride_elems) {
+  if (rows <= 0 || cols <= 0 || (cols % 8) || (row_stride_elems % 8)) return cudaErrorInvalidValue;
+  return tma::make_map_bf16_2d(reinterpret_cast<CUtensorMap*>(map), base, (uint64_t)rows,
+                               (uint64_t)cols, (uint64_t)row_stride_elems * 2, BM, BK);
+}
+
 // out[M, N] (bf16, rows `ldo` apart) = silu(x Wg^T) * (x Wu^T) for W = [Wg; ...; Wu from row
-// `up_offset` on; ...] with N rows each, over tensor maps of x [M, K] and W in boxes of 128
-// rows x 64 columns (`sakv_gemm_wide_map` makes them). K, N and ldo multiples of 8, out
+// `up_offset` on; ...] with N rows each, over tensor maps of x [M, K] and W from
+// sakv_gemm_pair_map. K, N and ldo multiples of 8, out
 // 16-byte aligned.
 SAKV_EXPORT int sakv_gemm_pair(const void* x_map, const void* w_map, int M, int N, int K,
                                int up_offset, void* out, long long ldo, cudaStream_t stream) {

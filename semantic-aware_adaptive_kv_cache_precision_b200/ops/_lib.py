@@ -54,6 +54,7 @@ PLAIN_SIGNATURES = {
     "sakv_prefill_attention_tc_qmap": ("attention_prefill_tc", [P, P, L, L, L]),
     "sakv_gemm_tc_map": ("gemm_tc", [P, P, L, L, L, I]),
     "sakv_gemm_wide_map": ("gemm_wide", [P, P, L, L, L]),
+    "sakv_gemm_pair_map": ("gemm_pair", [P, P, L, L, L]),
     "sakv_gemm_wide_error": ("gemm_wide", [P]),
     "sakv_gemm_pair_error": ("gemm_pair", [P]),
     "sakv_gemm_pair_resident": ("gemm_pair", []),

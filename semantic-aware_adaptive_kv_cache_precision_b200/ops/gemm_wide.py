@@ -69,22 +69,23 @@ def takes(x: torch.Tensor, weight: torch.Tensor) -> bool:
             and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0 and x.shape[0] > 0)
 
 
-def _make_map(t: torch.Tensor):
+def _make_map(t: torch.Tensor, maker: str = "sakv_gemm_wide_map"):
+    """(each kernel's library makes its own descriptors, so that only the library of the
+    kernel that runs is ever built)"""
     raw = ctypes.create_string_buffer(128 + 64)
     address = (ctypes.addressof(raw) + 63) & ~63
-    code = plain_function("sakv_gemm_wide_map")(address, t.data_ptr(), t.shape[0], t.shape[1],
-                                                t.stride(0))
+    code = plain_function(maker)(address, t.data_ptr(), t.shape[0], t.shape[1], t.stride(0))
     if code != 0:
         raise KernelError(f"could not make a TMA descriptor for a {tuple(t.shape)} matrix "
                           f"(error {code})")
     return raw, address
 
 
-def _weight_map(weight: torch.Tensor) -> int:
-    key = (weight.data_ptr(), tuple(weight.shape), weight.stride(), weight.dtype)
+def _weight_map(weight: torch.Tensor, maker: str = "sakv_gemm_wide_map") -> int:
+    key = (weight.data_ptr(), tuple(weight.shape), weight.stride(), weight.dtype, maker)
     hit = _weight_maps.get(key)
     if hit is None:
-        hit = _weight_maps[key] = _make_map(weight)
+        hit = _weight_maps[key] = _make_map(weight, maker)
     return hit[1]
 
 
@@ -106,8 +107,8 @@ def gated_pair(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
     if inter % 8:
         raise KernelError("gemm_wide.gated_pair: the intermediate size must be a multiple of 8")
     out = torch.empty((x.shape[0], inter), dtype=torch.bfloat16, device=x.device)
-    x_raw, x_map = _make_map(x)
-    call("sakv_gemm_pair", x_map, _weight_map(w_gate_up), x.shape[0], inter, x.shape[1], inter,
+    x_raw, x_map = _make_map(x, "sakv_gemm_pair_map")
+    call("sakv_gemm_pair", x_map, _weight_map(w_gate_up, "sakv_gemm_pair_map"), x.shape[0], inter, x.shape[1], inter,
          ptr(out), out.stride(0))
     return out
 
