@@ -97,6 +97,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap q_map,
   // 96.25 KB, so that two blocks fit an SM. The swizzled tiles need a 1024-byte aligned
   // base; a block that does not get one says so.
   extern __shared__ __align__(1024) uint8_t smem[];
+  let_next_kernel_start();
   if (tma::smem_u32(smem) & 1023) {
     if (threadIdx.x == 0 && error) atomicCAS(error, 0, 499);
     return;
@@ -131,17 +132,22 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap q_map,
     tma::fence_barrier_init();
   }
   if (warp == 1) tc::tmem_alloc(&bar->tmem, kTmemCols);
+  if (warp == 0 && lane == 0) {
+    tma::prefetch_map(&q_map);
+    tma::prefetch_map(&k_map);
+    tma::prefetch_map(&v_map);
+  }
   tc::fence_before_sync();
   __syncthreads();
   tc::fence_after_sync();
   const uint32_t tmem = bar->tmem;
+  // All of the above ran beside the end of the kernel before this one (the position kernel,
+  // which wrote the queries and the new keys and values); from here on its results are read.
+  wait_for_previous_kernel();
 
   if (warp == 0) {
     // ---- TMA ----------------------------------------------------------------------------
     if (lane == 0) {
-      tma::prefetch_map(&q_map);
-      tma::prefetch_map(&k_map);
-      tma::prefetch_map(&v_map);
       tma::mbar_expect_tx(&bar->q_full, kQBytes);
       tma::load_2d(q_s, &q_map, h * D, row0, &bar->q_full);
       tma::load_2d(q_s + QT * 128, &q_map, h * D + 64, row0, &bar->q_full);
@@ -355,8 +361,10 @@ constexpr int kFoldRows = 8;      // rows (warps) per block of the fold
 __global__ void fold_partials_kernel(const int4* __restrict__ folds, const float* __restrict__ part_o,
                                      const float* __restrict__ part_ml,
                                      __nv_bfloat16* __restrict__ out, int heads) {
-  const int4 f = folds[blockIdx.x / (QT / kFoldRows)];
+  let_next_kernel_start();
+  const int4 f = folds[blockIdx.x / (QT / kFoldRows)];      // (the step's plan: there before this step)
   const int h = blockIdx.y;
+  wait_for_previous_kernel();
   const int r = (blockIdx.x % (QT / kFoldRows)) * kFoldRows + (threadIdx.x >> 5);   // a warp per row
   if (r < f.w) {
     // A lane takes four of the row's 128 sizes (one 16-byte read a partial); the partials
@@ -447,16 +455,16 @@ SAKV_EXPORT int sakv_prefill_attention_tc(const void* q_map, const void* k_map, 
     if (e != cudaSuccess) return static_cast<int>(e);
     configured.done();
   }
-  prefill_attention_tc_kernel<<<dim3(heads, n_tiles), kThreads, kSmemBytes, stream>>>(
+  int status = launch_overlapped(
+      prefill_attention_tc_kernel, dim3(heads, n_tiles), dim3(kThreads), kSmemBytes, stream, 1,
       *(const CUtensorMap*)q_map, *(const CUtensorMap*)k_map, *(const CUtensorMap*)v_map,
       (__nv_bfloat16*)out, (const WorkItem*)q_tiles, part_o, part_ml, seq_lens, block_table,
       max_blocks, heads, kv_heads, scale * 1.4426950408889634f, window, error);
-  int status = launch_status();
-  if (status == 0 && n_folds > 0) {
-    fold_partials_kernel<<<dim3(n_folds * (QT / kFoldRows), heads), kFoldRows * 32, 0, stream>>>(
-        (const int4*)folds, part_o, part_ml, (__nv_bfloat16*)out, heads);
-    status = launch_status();
-  }
+  if (status == 0 && n_folds > 0)
+    status = launch_overlapped(fold_partials_kernel, dim3(n_folds * (QT / kFoldRows), heads),
+                               dim3(kFoldRows * 32), 0, stream, 1, (const int4*)folds,
+                               (const float*)part_o, (const float*)part_ml, (__nv_bfloat16*)out,
+                               heads);
   return status;
 }
 

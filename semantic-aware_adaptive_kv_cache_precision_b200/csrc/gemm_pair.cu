@@ -85,6 +85,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constan
   const int tiles = p.m_tiles * p.n_tiles;
   const int n_kb = (p.K + BK - 1) / BK;
 
+  let_next_kernel_start();
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
       tma::mbar_init(&bar->full[s], 1);
@@ -102,6 +103,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constan
   tma::cluster_sync_all();       // both blocks' barriers and tensor memory are there
   tc::fence_after_sync();
   const uint32_t tmem = bar->tmem;
+  // (the copy lane waits for the kernel before this one by itself, after its first weight
+  // boxes; everyone else here: nothing is written before that kernel is done)
+  if (threadIdx.x != 0) wait_for_previous_kernel();
 
   if (warp == 0) {
     // ---- TMA producer: this block's tokens and its half of the weight rows ---------------
@@ -110,21 +114,39 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constan
       tma::prefetch_map(&w_map);
       int stage = 0, phase = 0;
       bool ok = true;
+      // The weights do not depend on the kernel before this one (the norm that writes x):
+      // the weight boxes of the first tile's first stages are on their way before this lane
+      // waits for it, and only the boxes of x come after the wait.
+      const int early = pair < tiles ? min(kStages, n_kb) : 0;
+      {
+        const int n_tile = pair / p.m_tiles;
+        const int w_row = (rank == 0 ? 0 : p.up_offset) + n_tile * (BN / 2);
+        for (int kb = 0; kb < early; ++kb) {
+          const uint32_t full = tma::cluster_address(tma::smem_u32(&bar->full[kb]), 0);
+          if (rank == 0) tma::mbar_expect_tx(&bar->full[kb], 2 * kStageBytes);
+          tma::load_2d_pair(smem + kb * kStageBytes + kXBytes, &w_map, kb * BK, w_row, full);
+        }
+      }
+      wait_for_previous_kernel();
       for (int tile = pair; tile < tiles && ok; tile += pairs) {
         const int m_tile = tile % p.m_tiles, n_tile = tile / p.m_tiles;     // token tiles fastest
         const int x_row = (m_tile * 2 + static_cast<int>(rank)) * BM;
         const int w_row = (rank == 0 ? 0 : p.up_offset) + n_tile * (BN / 2);   // gate / up
         for (int kb = 0; kb < n_kb; ++kb) {
-          // (waiting for the parity before the ring's own: the first pass finds every stage free)
-          if (!tma::mbar_wait(&bar->empty[stage], phase ^ 1, p.error, 701)) {
-            ok = false;
-            break;
-          }
           uint8_t* dst = smem + stage * kStageBytes;
           const uint32_t full = tma::cluster_address(tma::smem_u32(&bar->full[stage]), 0);
-          if (rank == 0) tma::mbar_expect_tx(&bar->full[stage], 2 * kStageBytes);
-          tma::load_2d_pair(dst, &x_map, kb * BK, x_row, full);
-          tma::load_2d_pair(dst + kXBytes, &w_map, kb * BK, w_row, full);
+          if (tile == pair && kb < early) {          // (its weights are on their way)
+            tma::load_2d_pair(dst, &x_map, kb * BK, x_row, full);
+          } else {
+            // (waiting for the parity before the ring's own: the first pass finds every stage free)
+            if (!tma::mbar_wait(&bar->empty[stage], phase ^ 1, p.error, 701)) {
+              ok = false;
+              break;
+            }
+            if (rank == 0) tma::mbar_expect_tx(&bar->full[stage], 2 * kStageBytes);
+            tma::load_2d_pair(dst, &x_map, kb * BK, x_row, full);
+            tma::load_2d_pair(dst + kXBytes, &w_map, kb * BK, w_row, full);
+          }
           if (++stage == kStages) {
             stage = 0;
             phase ^= 1;
@@ -296,13 +318,15 @@ SAKV_EXPORT int sakv_gemm_pair(const void* x_map, const void* w_map, int M, int 
   config.blockDim = dim3(kThreads);
   config.dynamicSmemBytes = kSmemBytes;
   config.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 2;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;     // see common.cuh
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   config.attrs = attr;
-  config.numAttrs = 1;
+  config.numAttrs = 2;
   const cudaError_t e = cudaLaunchKernelEx(&config, gemm_pair_kernel,
                                            *reinterpret_cast<const CUtensorMap*>(x_map),
                                            *reinterpret_cast<const CUtensorMap*>(w_map), p);
