@@ -97,7 +97,6 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap q_map,
   // 96.25 KB, so that two blocks fit an SM. The swizzled tiles need a 1024-byte aligned
   // base; a block that does not get one says so.
   extern __shared__ __align__(1024) uint8_t smem[];
-  let_next_kernel_start();
   if (tma::smem_u32(smem) & 1023) {
     if (threadIdx.x == 0 && error) atomicCAS(error, 0, 499);
     return;
@@ -141,6 +140,9 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap q_map,
   __syncthreads();
   tc::fence_after_sync();
   const uint32_t tmem = bar->tmem;
+  // (with its shared and tensor memory in hand: a successor that waits on this SM can never
+  // hold what this block still needs)
+  let_next_kernel_start();
   // All of the above ran beside the end of the kernel before this one (the position kernel,
   // which wrote the queries and the new keys and values); from here on its results are read.
   wait_for_previous_kernel();

@@ -85,7 +85,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constan
   const int tiles = p.m_tiles * p.n_tiles;
   const int n_kb = (p.K + BK - 1) / BK;
 
-  let_next_kernel_start();
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
       tma::mbar_init(&bar->full[s], 1);
@@ -103,6 +102,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constan
   tma::cluster_sync_all();       // both blocks' barriers and tensor memory are there
   tc::fence_after_sync();
   const uint32_t tmem = bar->tmem;
+  // (only now, with its shared and tensor memory in hand: a successor that waits on an SM
+  // can then never hold what this block still needs)
+  let_next_kernel_start();
   // (the copy lane waits for the kernel before this one by itself, after its first weight
   // boxes; everyone else here: nothing is written before that kernel is done)
   if (threadIdx.x != 0) wait_for_previous_kernel();
