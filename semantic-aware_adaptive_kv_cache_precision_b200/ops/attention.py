@@ -97,8 +97,8 @@ def attention_decode(qkv: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Te
         raise KernelError("attention_decode: one length and one block list per sequence")
     if splits is None:
         splits = decode_splits(sequences, kv_heads, max_len)
-    if in_cluster is None:
-        in_cluster = splits in FOLD_IN_CLUSTER
+    if in_cluster is None:      # (a device that places no such cluster: the second kernel)
+        in_cluster = splits in FOLD_IN_CLUSTER and splits <= fold_cluster_limit(head_dim)
     if in_cluster and not 1 < splits <= fold_cluster_limit(head_dim):
         if splits > 1:
             raise KernelError(f"attention_decode: {splits} splits do not fold as one cluster "
