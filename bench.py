@@ -449,7 +449,7 @@ def main() -> int:
         read = []
 
         def one(chosen):
-            chosen = sampling.choose(engine.step(slots, device_tokens=chosen), greedy)
+            chosen = engine.next_tokens(slots, chosen)      # a greedy step, as generate runs it
             host = torch.empty((batch,), dtype=torch.int32, pin_memory=True)
             host.copy_(chosen, non_blocking=True)
             read.append(host)

@@ -16,7 +16,7 @@ from pathlib import Path
 import numpy as np
 import torch
 
-from .. import sampling
+from .. import ops, sampling
 from ..ops import _lib
 from ..cache import BLOCK, CacheFull, SequenceCache
 from ..config import config_from_dict, config_from_folder
@@ -191,9 +191,19 @@ class Engine:
         """End sequences; what they hold goes back to the cache."""
         self._need_cache().close(slots)
 
+    def next_tokens(self, slots: list, device_tokens: torch.Tensor) -> torch.Tensor:
+        """One greedy decode step: feed `device_tokens[i]` (int32 [len(slots)], on the device)
+        to the sequence in `slots[i]` and return the token each sequence chooses next, int32
+        [len(slots)] on the device, VALID UNTIL THE NEXT STEP of this engine (copy it, or
+        start its copy to the host, before that). It is `sampling.choose(step(slots,
+        device_tokens=...))` with the choice inside the step's captured graph: the tokens are
+        written where the next step reads its tokens, so feeding a call with what the call
+        before returned copies nothing, and the logits are not copied out of the graph."""
+        return self.step(slots, device_tokens=device_tokens, _greedy=True)
+
     def step(self, slots: list, new_tokens: list | None = None, want: list | None = None, *,
              device_tokens: torch.Tensor | None = None,
-             hidden_states: list | None = None) -> torch.Tensor:
+             hidden_states: list | None = None, _greedy: bool = False) -> torch.Tensor:
         """Feed `new_tokens[i]` to the sequence in `slots[i]`, after what its cache
         already holds, all sequences as one batch. Returns fp32 logits
         [wanted, vocab] on the device for `want[i]`, the places among
@@ -249,7 +259,10 @@ class Engine:
                     (0, self.spec.vocab_size), dtype=torch.float32, device=self.device)
             elif self.cuda_graphs and self.model.graph_safe and ctx.is_decode \
                     and rows == list(range(len(slots))):
-                logits = self._decode_by_graph(ctx, cache)
+                logits = self._decode_by_graph(ctx, cache, _greedy)
+                if _greedy:                      # (tokens, chosen inside the graph)
+                    cache.advance(slots, ends)
+                    return logits
             elif self.cuda_graphs and self.model.graph_safe and 0 < len(rows) <= 64 \
                     and ctx.tokens <= self.prefill_graph_tokens:
                 logits = self._prefill_by_graph(ctx, cache, (tuple(counts), tuple(starts),
@@ -259,7 +272,7 @@ class Engine:
                 logits = self.model.logits(x, ctx.want) if rows else torch.empty(
                     (0, self.spec.vocab_size), dtype=torch.float32, device=self.device)
             cache.advance(slots, ends)
-            return logits
+            return ops.choose(logits) if _greedy else logits
 
     @staticmethod
     def _slots_in_key(ctx, cache) -> tuple:
@@ -272,15 +285,22 @@ class Engine:
         the next: a part whose launches depend on them is not `graph_safe`.)"""
         return tuple(ctx.host_slots) if cache.states else ()
 
-    def _decode_by_graph(self, ctx, cache) -> torch.Tensor:
+    def _decode_by_graph(self, ctx, cache, greedy: bool = False) -> torch.Tensor:
         """Run a decode step through the CUDA graph of its shape (batch size and width of
         the block lists), capturing it the first time the shape comes up after one
-        decode step has run eagerly (which loads and configures every kernel)."""
+        decode step has run eagerly (which loads and configures every kernel). With `greedy`
+        the graph also chooses each sequence's next token and writes it into the step's own
+        token field (`ctx.token_ids`, the same device address in every step of the shape),
+        which is returned instead of the logits."""
+        def run():
+            logits = self.model.logits(self.model.hidden(ctx, cache), ctx.want)
+            return ops.choose(logits, out=ctx.token_ids) if greedy else logits
+
         if not self._decode_ran_eagerly:
             self._decode_ran_eagerly = True
-            return self.model.logits(self.model.hidden(ctx, cache), ctx.want)
+            return run()
         key = (ctx.sequences, tuple(tuple(t.shape) for t in ctx.tables), self._stager.generation,
-               self._slots_in_key(ctx, cache))
+               self._slots_in_key(ctx, cache), greedy)
         entry = self._graphs.get(key)
         if entry is None:
             if len(self._graphs) >= 64:                 # shapes come and go; keep the table small
@@ -292,7 +312,7 @@ class Engine:
             before = _lib.launches
             try:
                 with torch.cuda.graph(graph, pool=self._graph_pool):
-                    out = self.model.logits(self.model.hidden(ctx, cache), ctx.want)
+                    out = run()
             except Exception as exc:
                 self.graph_failure = repr(exc)      # kept for whoever wants to know why
                 # A part of this model does something a graph cannot hold (it reads a value
@@ -305,13 +325,13 @@ class Engine:
                     torch.cuda.synchronize(self.device)
                 except Exception:
                     pass
-                return self.model.logits(self.model.hidden(ctx, cache), ctx.want)
+                return run()
             entry = (graph, out, _lib.launches - before)
             self._graphs[key] = entry
             _lib.launches = before
         entry[0].replay()
         _lib.launches += entry[2]            # the kernels of this library inside the graph
-        return entry[1].clone()
+        return ctx.token_ids if greedy else entry[1].clone()
 
     def _prefill_by_graph(self, ctx, cache, shape) -> torch.Tensor:
         """A step that is not a decode step, through a CUDA graph once its shape (how many
@@ -538,7 +558,10 @@ class Engine:
                 tokens = feed.tokens
                 if len(rows) != tokens.shape[0]:
                     tokens = tokens[torch.as_tensor(rows, dtype=torch.long, device=self.device)]
-                out = self.step([slot_of[r.index] for r in step_requests], device_tokens=tokens)
+                step_slots = [slot_of[r.index] for r in step_requests]
+                if params.temperature == 0.0:          # the choice is part of the captured step
+                    return self._on_its_way(self.next_tokens(step_slots, tokens))
+                out = self.step(step_slots, device_tokens=tokens)
                 return self._choose(out, params, step_requests)
 
             decode_ahead(live, first, max_new_tokens, stops, launch, self._read,
@@ -553,8 +576,11 @@ class Engine:
     def _choose(self, logits, params, live) -> "_Chosen":
         """A token for each row of `logits`, chosen on the device; its copy to the host is
         on its way (pinned memory) but nothing waits for it here."""
-        tokens = sampling.choose(logits, params, [r.index for r in live],
-                                 [r.drawn for r in live])
+        return self._on_its_way(sampling.choose(logits, params, [r.index for r in live],
+                                                [r.drawn for r in live]))
+
+    @staticmethod
+    def _on_its_way(tokens: torch.Tensor) -> "_Chosen":
         host = torch.empty(tokens.shape, dtype=torch.int32, pin_memory=True)
         host.copy_(tokens, non_blocking=True)
         done = torch.cuda.Event()

@@ -75,7 +75,9 @@ class StepStager:
               device_tokens: torch.Tensor | None = None) -> StepContext:
         """`new_tokens[i]`: the tokens sequence i brings; `starts[i]`: its length
         before the step; with `device_tokens` (int32 [B] on the device, one token a sequence)
-        the ids are taken from there, on the stream, and `new_tokens` gives the counts only;
+        the ids are taken from there, on the stream, and `new_tokens` gives the counts only
+        (if they ARE this stager's own token field, where a captured step's choice of tokens
+        was written, they stay where they are and nothing is copied over them);
         `want_rows`: flat token rows whose logits are wanted;
         `tables[g]`: numpy int32 [B, max_blocks] of cache group g."""
         B = len(slots)
@@ -120,11 +122,14 @@ class StepStager:
         put("want", want_rows)
         for g, t in enumerate(tables):
             put(f"table{g}", t)
-        self.last_bytes = 4 * total
-        self.dev[:total].copy_(self.hosts[turn][:total], non_blocking=True)
+        in_place = (device_tokens is not None and offsets["token_ids"] == 0
+                    and device_tokens.data_ptr() == self.dev.data_ptr())
+        first = offsets["positions"] if in_place else 0      # (the token field comes first)
+        self.last_bytes = 4 * (total - first)
+        self.dev[first:total].copy_(self.hosts[turn][first:total], non_blocking=True)
         self.copied[turn] = torch.cuda.Event()
         self.copied[turn].record()
-        if device_tokens is not None:
+        if device_tokens is not None and not in_place:
             self.dev[offsets["token_ids"]:offsets["token_ids"] + T].copy_(device_tokens)
 
         def view(name, n):

@@ -165,10 +165,12 @@ def scale_cap_(x: torch.Tensor, scale: float = 1.0, cap: float | None = None) ->
 
 
 def choose(logits: torch.Tensor, temperature: float = 0.0, seed: int = 0,
-           request: torch.Tensor | None = None, step: torch.Tensor | None = None) -> torch.Tensor:
+           request: torch.Tensor | None = None, step: torch.Tensor | None = None,
+           out: torch.Tensor | None = None) -> torch.Tensor:
     """One token id per row of fp32 `logits`: greedy at temperature 0, else a
-    Gumbel-max draw keyed by (seed, request[row], step[row])."""
-    require_cuda(logits, request, step)
+    Gumbel-max draw keyed by (seed, request[row], step[row]). `out` (int32 [rows], contiguous):
+    where to write them, instead of a new tensor."""
+    require_cuda(logits, request, step, out)
     _check(logits.dtype == torch.float32 and logits.dim() == 2 and logits.stride(1) == 1,
            "logits: fp32 [rows, vocab]")
     rows, vocab = logits.shape
@@ -176,7 +178,11 @@ def choose(logits: torch.Tensor, temperature: float = 0.0, seed: int = 0,
         for t, name in ((request, "request"), (step, "step")):
             _check(t is not None and t.dtype == torch.int32 and t.is_contiguous()
                    and t.numel() == rows, f"{name}: int32 [rows]")
-    out = torch.empty((rows,), dtype=torch.int32, device=logits.device)
+    if out is None:
+        out = torch.empty((rows,), dtype=torch.int32, device=logits.device)
+    else:
+        _check(out.dtype == torch.int32 and out.shape == (rows,) and out.is_contiguous(),
+               "out: int32 [rows]")
     chunks = plain_function("sakv_choose_chunks")(vocab)
     scratch = _choose_scratch.get(logits.device)
     if scratch is None or scratch[0].numel() < rows * chunks or scratch[1].numel() < rows:

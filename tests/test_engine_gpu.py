@@ -635,3 +635,50 @@ def test_random_schedules_give_the_logits_of_whole_prompts(name, dtype, engines)
             engine.close([live.pop(r)[0] for r in done])
         engine.cache.check()
     assert engine.cache.slots.held == 0 and all(g.pool.held == 0 for g in engine.cache.groups)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["B", "D"])
+def test_next_tokens_is_a_step_and_its_greedy_choice(name, dtype, varied_folders):
+    """`Engine.next_tokens` (the choice inside the captured step, the tokens left where the
+    next step reads them) gives what `step` followed by the greedy choice gives, step after
+    step: fed with its own result (nothing copied), with a copy of it, with a batch that
+    shrinks, and after another step has used the staging buffer in between."""
+    from semantic_aware_adaptive_kv_cache_precision_b200 import sampling
+    folder = varied_folders(name, stored(dtype))
+    two = [engine_for(folder, dtype) for _ in range(2)]
+    prompts = prompts_for(name, [70, 5, 130, 64], seed=5)
+    greedy = sampling.SamplingParams()
+    fed, slots = [], []
+    for engine in two:
+        s = engine.open(len(prompts))
+        logits = engine.step(s, prompts)
+        fed.append(sampling.choose(logits, greedy))
+        slots.append(s)
+    assert torch.equal(fed[0], fed[1])
+    live = list(range(len(prompts)))
+    history = []
+    for t in range(40):
+        a = two[0].next_tokens([slots[0][i] for i in live], fed[0])
+        b = sampling.choose(two[1].step([slots[1][i] for i in live], device_tokens=fed[1]), greedy)
+        assert torch.equal(a, b), f"step {t}: {a.tolist()} against {b.tolist()}"
+        history.append(a.tolist())
+        fed = [a, b]
+        if t % 7 == 3:
+            fed[0] = a.clone()                        # not the engine's own buffer
+        if t == 10:                                   # another step uses the staging buffer
+            kept = a.clone()
+            (other,) = two[0].open(1)
+            two[0].step([other], [prompts[0][:9]])
+            two[0].close([other])
+            fed[0] = kept
+        if t in (15, 25):                             # a request leaves
+            gone = live.pop(1)
+            for engine, s in zip(two, slots):
+                engine.close([s[gone]])
+            keep = torch.as_tensor([j for j in range(len(live) + 1) if j != 1], device=a.device)
+            fed = [f[keep] for f in fed]
+    assert len({tuple(h) for h in history}) > 10      # (the tokens do vary)
+    for engine, s in zip(two, slots):
+        engine.close([s[i] for i in live])
+        assert engine.cache.slots.held == 0
